@@ -1,0 +1,172 @@
+"""Generate the golden fixtures in this directory from the reference's own Python code.
+
+Run once, in a container that has the reference checkout (path in $SORTNET_REFERENCE,
+default /root/reference):   python tests/golden/make_golden.py
+
+The reference's pure-PyTorch branches are imported unmodified with an empty stand-in for
+its CUDA extension module, evaluated on CPU on small seeded inputs, and their outputs and
+autograd gradients are stored as .npz files.  The tests then check the CPU oracle (and,
+through it, the CUDA kernels) against these files; nothing at test time reads the
+reference checkout.
+
+Branches used: core/norm_dist.py:180-185 (norm_dist), :194-213 (norm_dist_dropout, with the
+inner norm_dist call forced onto the PyTorch branch), :224-230 (sort_neuron), :250-259
+(bound_inf_dist); core/models/bound_basic_module.py:123-157 (MeanShiftDropout);
+core/models/norm_dist.py:14-17 (sample_mask).
+"""
+import functools
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+REF = os.environ.get("SORTNET_REFERENCE", "/root/reference")
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+sys.modules["norm_dist_cuda"] = types.ModuleType("norm_dist_cuda")
+sys.path.insert(0, REF)
+import core.norm_dist as ref_ops  # noqa: E402
+from core.models.bound_basic_module import MeanShiftDropout  # noqa: E402
+from core.models.norm_dist import sample_mask  # noqa: E402
+
+INF = float("inf")
+
+
+def gen(seed, B, CI, CO):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.rand(B, CI, generator=g)
+    w = torch.randn(CO, CI, generator=g)
+    gy = torch.randn(B, CO, generator=g)
+    return x, w, gy
+
+
+def no_ties_inf(x, w):
+    d = (x[:, None, :] - w[None]).abs()
+    top2 = d.topk(2, dim=-1)[0]
+    return bool((top2[..., 0] > top2[..., 1]).all())
+
+
+def case_norm_dist(seed, B, CI, CO, p):
+    x, w, gy = gen(seed, B, CI, CO)
+    if p == INF:
+        assert no_ties_inf(x, w), "pick another seed: tie in the max"
+    x3 = x.unsqueeze(-1).requires_grad_()
+    wp = w.clone().requires_grad_()
+    y = ref_ops.norm_dist(x3, wp, p, use_custom_cuda_func=False)
+    y.backward(gy.unsqueeze(-1))
+    return dict(x=x, w=w, gy=gy, p=np.float64(p), y=y.detach().squeeze(-1),
+                gx=x3.grad.squeeze(-1), gw=wp.grad)
+
+
+def case_dropout(seed, B, CI_full, CO_full, q, p):
+    torch.manual_seed(seed)
+    S = (B - 1) // 32 + 1
+    ci = sample_mask(S, 1, CI_full, q, device="cpu")
+    co = sample_mask(S, 1, CO_full, q, device="cpu")
+    g = torch.Generator().manual_seed(seed + 1000)
+    x = torch.rand(B, ci.size(-1), generator=g)
+    w = torch.randn(CO_full, CI_full, generator=g)
+    gy = torch.randn(B, co.size(-1), generator=g)
+    x3 = x.unsqueeze(-1).requires_grad_()
+    wp = w.clone().requires_grad_()
+    saved = ref_ops.norm_dist
+    ref_ops.norm_dist = functools.partial(saved, use_custom_cuda_func=False)
+    try:
+        y = ref_ops.norm_dist_dropout(x3, wp, ci, co, p, use_custom_cuda_func=False)
+    finally:
+        ref_ops.norm_dist = saved
+    y.backward(gy.unsqueeze(-1))
+    if p == INF:
+        for s in range(S):
+            ws = w[co[s, 0].long()][:, ci[s, 0].long()]
+            assert no_ties_inf(x[s * 32:(s + 1) * 32], ws), "pick another seed"
+    return dict(x=x, w=w, gy=gy, p=np.float64(p), ci=ci[:, 0], co=co[:, 0],
+                y=y.detach().squeeze(-1), gx=x3.grad.squeeze(-1), gw=wp.grad)
+
+
+def case_bound(seed, B, CI, CO, eps):
+    x, w, gl = gen(seed, B, CI, CO)
+    gu = torch.randn(B, CO, generator=torch.Generator().manual_seed(seed + 7))
+    xl = (x - eps).clamp(0, 1)
+    xu = (x + eps).clamp(0, 1)
+    l3 = xl.unsqueeze(-1).requires_grad_()
+    u3 = xu.unsqueeze(-1).requires_grad_()
+    wp = w.clone().requires_grad_()
+    yl, yu = ref_ops.bound_inf_dist(l3, u3, wp, use_custom_cuda_func=False)
+    # uniqueness of the extremal coordinate, so autograd and the index rule agree
+    x1 = w[None] - xl[:, None, :]
+    x2 = xu[:, None, :] - w[None]
+    hi = torch.maximum(x1, x2).topk(2, dim=-1)[0]
+    lo = (-torch.minimum(x1, x2)).topk(2, dim=-1)[0]
+    assert bool((hi[..., 0] > hi[..., 1]).all()) and bool((lo[..., 0] > lo[..., 1]).all())
+    assert bool((x1 != x2).all())
+    (yl * gl.unsqueeze(-1)).sum().add((yu * gu.unsqueeze(-1)).sum()).backward()
+    return dict(xl=xl, xu=xu, w=w, gl=gl, gu=gu, yl=yl.detach().squeeze(-1),
+                yu=yu.detach().squeeze(-1), gxl=l3.grad.squeeze(-1), gxu=u3.grad.squeeze(-1),
+                gw=wp.grad)
+
+
+def case_sort(seed, B, CI, CO, q, K):
+    x, w, _ = gen(seed, B, CI, CO)
+    y = ref_ops.sort_neuron(x.unsqueeze(-1), w, q=q, truncate=K, use_custom_cuda_func=False)
+    return dict(x=x, w=w, q=np.float64(q), K=np.int64(K), y=y.squeeze(-1))
+
+
+def case_mean_shift(seed, B, C_full, q):
+    torch.manual_seed(seed)
+    S = (B - 1) // 32 + 1
+    out = {}
+    m = MeanShiftDropout(C_full, affine=False)
+    m.running_mean.copy_(torch.randn(C_full))
+    out["running_mean0"] = m.running_mean.clone()
+    if q is None:
+        index = None
+        C = C_full
+    else:
+        index = sample_mask(S, 1, C_full, q, device="cpu")
+        C = index.size(-1)
+        out["index"] = index[:, 0]
+    x = torch.randn(B, C, 1, requires_grad=True)
+    gy = torch.randn(B, C, 1)
+    m.train()
+    y, _, _ = m(x, None, None, index=None if index is None else index.long())
+    y.backward(gy)
+    out.update(x=x.detach().squeeze(-1), gy=gy.squeeze(-1), y=y.detach().squeeze(-1),
+               gx=x.grad.squeeze(-1), running_mean1=m.running_mean.clone())
+    m.eval()
+    lo = x.detach() - 0.1
+    up = x.detach() + 0.2
+    if index is None:
+        ye, le, ue = m(x.detach(), lo, up)
+        out.update(eval_y=ye.squeeze(-1), eval_l=le.squeeze(-1), eval_u=ue.squeeze(-1))
+    return out
+
+
+def save(name, d):
+    arrs = {k: (v.detach().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in d.items()}
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrs)
+    print(name, {k: tuple(a.shape) for k, a in arrs.items()})
+
+
+def main():
+    torch.set_num_threads(8)
+    save("norm_dist_inf_a", case_norm_dist(0, 70, 48, 40, INF))
+    save("norm_dist_inf_b", case_norm_dist(1, 33, 17, 5, INF))
+    save("norm_dist_p2", case_norm_dist(2, 37, 29, 21, 2.0))
+    save("norm_dist_p8", case_norm_dist(3, 70, 48, 40, 8.0))
+    save("norm_dist_p31", case_norm_dist(4, 40, 50, 24, 31.6))
+    save("norm_dist_p3", case_norm_dist(5, 19, 23, 11, 3.0))
+    save("dropout_inf", case_dropout(10, 70, 48, 40, 0.8, INF))
+    save("dropout_p8", case_dropout(11, 70, 48, 40, 0.8, 8.0))
+    save("dropout_p20", case_dropout(12, 45, 30, 36, 0.7, 20.0))
+    save("bound_a", case_bound(20, 70, 48, 40, 0.3))
+    save("bound_b", case_bound(21, 33, 17, 5, 0.03))
+    save("sort_a", case_sort(30, 20, 48, 12, 0.6, 10))
+    save("mean_shift_masked", case_mean_shift(40, 70, 40, 0.8))
+    save("mean_shift_plain", case_mean_shift(41, 45, 24, None))
+
+
+if __name__ == "__main__":
+    main()
