@@ -1,0 +1,143 @@
+/*
+ * sortnet_b200 — C ABI of the B200 (sm_100a) norm-distance neuron kernels.
+ *
+ * Drop-in boundary: these entry points are what a binding for the `norm_dist_cuda`
+ * extension module of zbh2047/SortNet (core/cuda/norm_dist.cpp:294-318) calls instead of
+ * the static launchers declared in core/cuda/norm_dist.h:4-60.  Argument order follows
+ * those launchers: inputs, sizes (B, CO, CI, G, HW), outputs, optional index lists with the
+ * full weight shape (W_CO, W_CI); a CUDA stream handle is appended.
+ *
+ * Conventions
+ *   - All pointers are device pointers to contiguous fp32 / int32 arrays owned by the
+ *     caller; nothing is allocated or freed here.  Outputs are overwritten; gradient
+ *     buffers are zero-filled by the backward entry points before they scatter into them
+ *     (the reference launchers do the same, e.g. inf_dist_cuda.cu:332,348-349).
+ *   - Shapes: x [B, CI, HW], w [W_CO, W_CI / G], y [B, CO, HW].  Only G == 1 and HW == 1
+ *     are implemented (every fully connected SortNet layer); anything else returns
+ *     SNB_STATUS_UNSUPPORTED.
+ *   - Index lists (`w_index_ci` [S, CI], `w_index_co` [S, CO], S = ceil(B / 32), sorted
+ *     int32, may be NULL) select, for each 32-row sub-batch, the columns / rows of w that the
+ *     compact x / y correspond to (core/models/norm_dist.py:14-17; inf_dist_cuda.cu:123,166-169).
+ *   - `stream` is a cudaStream_t (NULL = legacy default stream).  Work is enqueued on it and
+ *     the call returns without synchronising.  Entry points are re-entrant and keep no
+ *     mutable global state besides cached device attributes.
+ *   - Return value: 0 on success, otherwise one of the SNB_STATUS_* codes below;
+ *     snb_status_string() describes it and snb_last_cuda_error() gives the CUDA runtime
+ *     message after SNB_STATUS_CUDA.  The reference launchers return void and check nothing.
+ */
+#ifndef SORTNET_B200_H
+#define SORTNET_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SNB_STATUS_OK 0
+#define SNB_STATUS_NULL_POINTER 1
+#define SNB_STATUS_BAD_SHAPE 2
+#define SNB_STATUS_UNSUPPORTED 3
+#define SNB_STATUS_TOO_LARGE 4
+#define SNB_STATUS_CUDA 5
+#define SNB_STATUS_ALIGNMENT 6
+
+const char* snb_status_string(int status);
+const char* snb_last_cuda_error(void);
+int snb_version(void);
+
+/* ---- l-infinity distance ---------------------------------------------------------------- */
+
+/* y[b,j] = max(1e-10, max_c |x[b,c] - w[co[s][j], ci[s][c]]|), pos[b,j] = lowest such c, bit 31
+ * set when x - w < 0; pos = 0 when nothing exceeds 1e-10.
+ * Replaces inf_dist::forward (norm_dist.h:24-26; inf_dist_cuda.cu:306-323). */
+int snb_inf_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                         float* y, int* pos, const int* w_index_ci, const int* w_index_co,
+                         int W_CO, int W_CI, void* stream);
+
+/* Same y without pos, unmasked.  Replaces inf_dist::forward_nograd (norm_dist.h:22-23;
+ * inf_dist_cuda.cu:277-304). */
+int snb_inf_dist_forward_nograd(const float* x, const float* w, int B, int CO, int CI, int G,
+                                int HW, float* y, void* stream);
+
+/* grad_input[b, idx] += s * grad_output[b,j] with (idx, s) decoded from pos.
+ * Replaces inf_dist::backward_input (norm_dist.h:27-28; inf_dist_cuda.cu:325-336). */
+int snb_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI,
+                                int G, int HW, float* grad_input, void* stream);
+
+/* As above plus grad_weight[co[s][j], ci[s][idx]] -= s * grad_output[b,j]; grad_weight is the
+ * full [W_CO, W_CI] matrix.  Replaces inf_dist::backward_input_weight (norm_dist.h:29-31;
+ * inf_dist_cuda.cu:338-354). */
+int snb_inf_dist_backward_input_weight(const float* grad_output, const int* pos, int B, int CO,
+                                       int CI, int G, int HW, float* grad_input,
+                                       float* grad_weight, const int* w_index_ci,
+                                       const int* w_index_co, int W_CO, int W_CI, void* stream);
+
+/* ---- l-p distance, finite p ----------------------------------------------------------------- */
+
+/* p <= 10: y = max(sum_c |t|^p, FLT_MIN)^(1/p); p > 10: y = M (sum_c (|t|/M)^p + (1e-10/M)^p)^(1/p)
+ * with M = max(1e-10, max_c |t|), t = x - w.  Integer p in [1, 8] uses multiply chains.
+ * Replaces norm_dist<ip>::forward and ::forward_with_max(max_output = NULL) behind the p
+ * dispatch of core/cuda/norm_dist.cpp:43-65 (norm_dist.h:5-10; norm_dist_cuda.cu:511-551). */
+int snb_norm_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                          float* y, float p, const int* w_index_ci, const int* w_index_co,
+                          int W_CO, int W_CI, void* stream);
+
+/* grad_input[b,c] = sum_j g[b,j] sgn(t) (|t| / y[b,j])^(p-1).
+ * Replaces norm_dist<ip>::backward_input (norm_dist.h:11-13; norm_dist_cuda.cu:553-572). */
+int snb_norm_dist_backward_input(const float* grad_output, const float* x, const float* w,
+                                 const float* y, int B, int CO, int CI, int G, int HW,
+                                 float* grad_input, float p, const int* w_index_ci,
+                                 const int* w_index_co, int W_CO, int W_CI, void* stream);
+
+/* As above plus grad_weight[co[s][j], ci[s][c]] -= the same terms summed over the sub-batch.
+ * Replaces norm_dist<ip>::backward_input_weight (norm_dist.h:14-18; norm_dist_cuda.cu:574-594). */
+int snb_norm_dist_backward_input_weight(const float* grad_output, const float* x, const float* w,
+                                        const float* y, int B, int CO, int CI, int G, int HW,
+                                        float* grad_input, float* grad_weight, float p,
+                                        const int* w_index_ci, const int* w_index_co, int W_CO,
+                                        int W_CI, void* stream);
+
+/* ---- interval bounds through an l-infinity layer ------------------------------------------- */
+
+/* yL = -min(-1e-10, min_c min(w - xL, xU - w)), yU = max(1e-10, max_c max(w - xL, xU - w)); an
+ * inverted interval (xL > xU) is replaced by its midpoint.
+ * Replaces bound_inf_dist::forward_nograd (norm_dist.h:35-36; bound_inf_dist_cuda.cu:314-328). */
+int snb_bound_inf_dist_forward_nograd(const float* xl, const float* xu, const float* w, int B,
+                                      int CO, int CI, int G, int HW, float* yl, float* yu,
+                                      void* stream);
+
+/* Same bounds plus the words of the coordinates that set them: c | (bit 31 when w - xL > xU - w);
+ * posL = 0xffffffff when the lower bound stayed at its floor (no gradient), posU defaults to 0.
+ * Replaces bound_inf_dist::forward (norm_dist.h:37-38; bound_inf_dist_cuda.cu:330-345). */
+int snb_bound_inf_dist_forward(const float* xl, const float* xu, const float* w, int B, int CO,
+                               int CI, int G, int HW, float* yl, float* yu, int* posl, int* posu,
+                               void* stream);
+
+/* Sparse backward of the bounds.  Replaces bound_inf_dist::backward_input and
+ * ::backward_input_weight (norm_dist.h:39-44; bound_inf_dist_cuda.cu:362-383). */
+int snb_bound_inf_dist_backward_input(const float* grad_yl, const float* grad_yu, const int* posl,
+                                      const int* posu, int B, int CO, int CI, int G, int HW,
+                                      float* grad_xl, float* grad_xu, void* stream);
+int snb_bound_inf_dist_backward_input_weight(const float* grad_yl, const float* grad_yu,
+                                             const int* posl, const int* posu, int B, int CO, int CI,
+                                             int G, int HW, float* grad_xl, float* grad_xu,
+                                             float* grad_w, void* stream);
+
+/* ---- mean shift ------------------------------------------------------------------------------ */
+
+/* mean[c] (c < C_full) = mean of x[b, slot(c)] over the rows whose sub-batch kept channel c
+ * (index [S, C] sorted int32, NULL = all channels, then C_full == C); 0 for never-kept channels.
+ * When running_mean is not NULL it is updated as (1 - momentum) * running_mean + momentum * mean.
+ * Replaces the training branch of MeanShiftDropout.forward
+ * (core/models/bound_basic_module.py:125-144), which is PyTorch code in the reference. */
+int snb_mean_shift_stats(const float* x, const int* index, int B, int C, int C_full, float* mean,
+                         float* running_mean, float momentum, void* stream);
+
+/* y[b,j] = x[b,j] - mean[index[s_b][j]] (index NULL = identity); y may alias x.
+ * Replaces core/models/bound_basic_module.py:149-157. */
+int snb_mean_shift_apply(const float* x, const float* mean, const int* index, int B, int C,
+                         float* y, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SORTNET_B200_H */

@@ -1,0 +1,71 @@
+"""ctypes loader for libsortnet_b200.so (the C ABI declared in include/sortnet_b200.h)."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libsortnet_b200.so")
+
+_lib = None
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+
+# name -> argument types (every function returns int status)
+SIGNATURES = {
+    "snb_inf_dist_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
+    "snb_inf_dist_forward_nograd": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "snb_inf_dist_backward_input": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "snb_inf_dist_backward_input_weight": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
+    "snb_norm_dist_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P],
+    "snb_norm_dist_backward_input": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P],
+    "snb_norm_dist_backward_input_weight": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _I, _P],
+    "snb_bound_inf_dist_forward_nograd": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
+    "snb_bound_inf_dist_forward": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
+    "snb_bound_inf_dist_backward_input": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
+    "snb_bound_inf_dist_backward_input_weight": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "snb_mean_shift_stats": [_P, _P, _I, _I, _I, _P, _P, _F, _P],
+    "snb_mean_shift_apply": [_P, _P, _P, _I, _I, _P, _P],
+}
+
+
+class SortnetB200Error(RuntimeError):
+    pass
+
+
+def load(build_if_missing: bool = False):
+    """Loads the shared library once and declares the prototypes; raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        if build_if_missing:
+            from . import build as _build
+            _build.build()
+        else:
+            raise SortnetB200Error(
+                "libsortnet_b200.so is not built (run `python -m sortnet_b200.build`); "
+                "there is no CPU or PyTorch fallback for these operators")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = ctypes.c_int
+    lib.snb_status_string.argtypes = [ctypes.c_int]
+    lib.snb_status_string.restype = ctypes.c_char_p
+    lib.snb_last_cuda_error.argtypes = []
+    lib.snb_last_cuda_error.restype = ctypes.c_char_p
+    lib.snb_version.argtypes = []
+    lib.snb_version.restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str):
+    if status == 0:
+        return
+    lib = load()
+    msg = lib.snb_status_string(status).decode()
+    if status == 5:
+        msg += ": " + lib.snb_last_cuda_error().decode()
+    raise SortnetB200Error("%s failed: %s (status %d)" % (what, msg, status))

@@ -1,0 +1,369 @@
+// l-infinity distance neuron: forward (with / without argmax word, dense or index-masked)
+// and the sparse backward.
+//
+// Replaces zbh2047/SortNet core/cuda/inf_dist_cuda.cu (kernels :17-107, :110-212, :214-271;
+// launchers :277-354).  Results are identical to that file's: y = max(1e-10, max_c |x - w|)
+// bit for bit, pos = lowest c attaining the maximum | sign bit of (x - w), 0 when nothing
+// exceeds 1e-10.
+//
+// Forward = max-plus "GEMM": 8x8 outputs per thread, two reduction steps per instruction pair
+// (packed fp32 subtract on a register pair + three-input |.|-max into the accumulator).
+// The argmax is not tracked per element: the main loop only records, per output, the first
+// 64-wide chunk of the reduction axis in which the accumulator grew to its final value
+// (one compare per output per chunk); a second small kernel rescans that one chunk and
+// writes the exact word.  Strict '>' on chunk level followed by "first equal element"
+// inside the chunk is the same total order as the reference's strict '>' element scan.
+#include "tile.cuh"
+#include "launch.h"
+
+namespace snb {
+
+struct InfFwdParams {
+    const float* x;
+    const float* w;
+    float* y;
+    int* pos;       // TRACK: receives the chunk id (or -1), rewritten by the resolve kernel
+    const int* ci;  // [S][CI] kept columns of W per sub-batch, or null
+    const int* co;  // [S][CO] kept rows of W per sub-batch, or null
+    int B, CO, CI;  // compact sizes seen by x / y
+    int W_CI;       // leading dimension of w
+};
+
+constexpr int CHUNK_TILES = 2;  // argmax chunk = 2 k-tiles = 64 reduction steps
+
+enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
+
+template <int WM, int WN, int MODE, bool TRACK>
+__global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams p) {
+    constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
+    static_assert(MODE != MODE_GATHER || WM == 1, "masked tiles are one 32-row sub-batch");
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;                 // [2][BM][LDS]
+    float* ws = smem + 2 * BM * LDS;  // [2][BN][LDS]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp / WN, wn = warp % WN, tb = lane >> 3, tj = lane & 7;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int nk = (p.CI + BK - 1) / BK;
+
+    GatherW<BN, NT> gw;
+    const int* ci_s = nullptr;
+    if (MODE == MODE_GATHER) {
+        const int s = m0 / SNB_SUB_BATCH;
+        ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
+        gw.init_rows(p.co ? p.co + (size_t)s * p.CO : nullptr, n0, p.CO, p.W_CI, tid);
+        gw.fetch_cols(ci_s, 0, p.CI, tid);
+    }
+
+    auto stage = [&](int kt, int st) {
+        float* xd = xs + st * BM * LDS;
+        float* wd = ws + st * BN * LDS;
+        if (MODE == MODE_VEC) {
+            stage_dense_vec<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            stage_dense_vec<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
+        } else if (MODE == MODE_SCALAR) {
+            stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            stage_dense_scalar<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
+        } else {
+            stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            gw.stage(wd, p.w, tid);
+        }
+    };
+
+    float acc[8][8];
+    float prev[TRACK ? 8 : 1][TRACK ? 8 : 1];
+    uint32_t q[TRACK ? 8 : 1][TRACK ? 4 : 1];  // two 16-bit chunk ids per word, 0xffff = none
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = SNB_EPS;
+    if (TRACK) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) prev[i][j] = SNB_EPS;
+#pragma unroll
+            for (int j = 0; j < 4; j++) q[i][j] = 0xffffffffu;
+        }
+    }
+
+    stage(0, 0);
+    cp_async_commit();
+
+    for (int kt = 0; kt < nk; kt++) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (kt + 1 < nk) {
+            if (MODE == MODE_GATHER) {
+                gw.fetch_cols(ci_s, (kt + 1) * BK, p.CI, tid);
+            }
+            stage(kt + 1, (kt + 1) & 1);
+        }
+        cp_async_commit();
+
+        const float* xr = xs + (kt & 1) * BM * LDS + (wm * 32 + tb) * LDS;
+        const float* wr = ws + (kt & 1) * BN * LDS + (wn * 64 + tj) * LDS;
+#pragma unroll 2
+        for (int kk = 0; kk < BK / 4; kk++) {
+            ulonglong2 xf[8], wf[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                xf[i] = *reinterpret_cast<const ulonglong2*>(xr + i * 4 * LDS + kk * 4);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                wf[j] = *reinterpret_cast<const ulonglong2*>(wr + j * 8 * LDS + kk * 4);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float a, b;
+                    unpack2(sub2(xf[i].x, wf[j].x), a, b);
+                    acc[i][j] = max3abs(acc[i][j], a, b);
+                    unpack2(sub2(xf[i].y, wf[j].y), a, b);
+                    acc[i][j] = max3abs(acc[i][j], a, b);
+                }
+            }
+        }
+        if (TRACK && (((kt % CHUNK_TILES) == CHUNK_TILES - 1) || kt == nk - 1)) {
+            const uint32_t chunk = (uint32_t)(kt / CHUNK_TILES);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (acc[i][j] > prev[i][j])
+                        q[i][j >> 1] = (j & 1) ? __byte_perm(q[i][j >> 1], chunk, 0x5410)
+                                               : __byte_perm(q[i][j >> 1], chunk, 0x3254);
+                    prev[i][j] = acc[i][j];
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + wm * 32 + tb + 4 * i;
+        if (m >= p.B) continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int n = n0 + wn * 64 + tj + 8 * j;
+            if (n >= p.CO) continue;
+            const size_t o = (size_t)m * p.CO + n;
+            p.y[o] = acc[i][j];
+            if (TRACK) {
+                uint32_t c = (j & 1) ? (q[i][j >> 1] >> 16) : (q[i][j >> 1] & 0xffffu);
+                p.pos[o] = c == 0xffffu ? -1 : (int)c;
+            }
+        }
+    }
+}
+
+// Turns the chunk id left in pos by the tracking kernel into the reference's argmax word.
+__global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p) {
+    const int n = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int m = blockIdx.y * 8 + (threadIdx.x >> 5);
+    if (n >= p.CO || m >= p.B) return;
+    const size_t o = (size_t)m * p.CO + n;
+    const int chunk = p.pos[o];
+    if (chunk < 0) {
+        p.pos[o] = 0;
+        return;
+    }
+    const int s = m / SNB_SUB_BATCH;
+    const float yv = p.y[o];
+    const float* xr = p.x + (size_t)m * p.CI;
+    const float* wr = p.w + (size_t)(p.co ? p.co[(size_t)s * p.CO + n] : n) * p.W_CI;
+    const int* ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
+    const int c0 = chunk * (CHUNK_TILES * BK);
+    const int c1 = min(p.CI, c0 + CHUNK_TILES * BK);
+    uint32_t word = 0;
+    for (int c = c0; c < c1; c++) {
+        const float t = xr[c] - wr[ci_s ? ci_s[c] : c];
+        if (fabsf(t) == yv) {
+            word = (uint32_t)c | (t >= 0 ? 0u : SNB_SIGN_BIT);
+            break;
+        }
+    }
+    p.pos[o] = (int)word;
+}
+
+// Sparse backward: one CTA per batch row.  grad_x of the row is accumulated in shared
+// memory (many outputs of a row share an argmax column) and written once, so grad_x needs
+// neither a memset nor global atomics; grad_w gets one global reduction per output.
+__global__ void __launch_bounds__(256) inf_bwd_kernel(const float* __restrict__ g,
+                                                      const int* __restrict__ pos, int B, int CO,
+                                                      int CI, float* __restrict__ gx,
+                                                      float* __restrict__ gw,
+                                                      const int* __restrict__ ci,
+                                                      const int* __restrict__ co, int W_CI) {
+    extern __shared__ float row[];  // [CI]
+    const int b = blockIdx.x, s = b / SNB_SUB_BATCH;
+    for (int c = threadIdx.x; c < CI; c += blockDim.x) row[c] = 0.f;
+    __syncthreads();
+    const int* ci_s = ci ? ci + (size_t)s * CI : nullptr;
+    const int* co_s = co ? co + (size_t)s * CO : nullptr;
+    for (int j = threadIdx.x; j < CO; j += blockDim.x) {
+        const uint32_t pw = (uint32_t)pos[(size_t)b * CO + j];
+        const float gv = g[(size_t)b * CO + j];
+        const int idx = (int)(pw & ~SNB_SIGN_BIT);
+        const float v = (pw & SNB_SIGN_BIT) ? -gv : gv;
+        atomicAdd(&row[idx], v);
+        if (gw) {
+            const int r = co_s ? co_s[j] : j;
+            const int c = ci_s ? ci_s[idx] : idx;
+            atomicAdd(&gw[(size_t)r * W_CI + c], -v);
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < CI; c += blockDim.x) gx[(size_t)b * CI + c] = row[c];
+}
+
+// Same as above for rows too wide for shared memory: global atomics into a zeroed grad_x.
+__global__ void __launch_bounds__(256) inf_bwd_wide_kernel(const float* __restrict__ g,
+                                                           const int* __restrict__ pos, int B,
+                                                           int CO, int CI, float* __restrict__ gx,
+                                                           float* __restrict__ gw,
+                                                           const int* __restrict__ ci,
+                                                           const int* __restrict__ co, int W_CI) {
+    const int b = blockIdx.y, s = b / SNB_SUB_BATCH;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= CO) return;
+    const uint32_t pw = (uint32_t)pos[(size_t)b * CO + j];
+    const float gv = g[(size_t)b * CO + j];
+    const int idx = (int)(pw & ~SNB_SIGN_BIT);
+    const float v = (pw & SNB_SIGN_BIT) ? -gv : gv;
+    atomicAdd(&gx[(size_t)b * CI + idx], v);
+    if (gw) {
+        const int r = co ? co[(size_t)s * CO + j] : j;
+        const int c = ci ? ci[(size_t)s * CI + idx] : idx;
+        atomicAdd(&gw[(size_t)r * W_CI + c], -v);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+template <int WM, int WN, int MODE, bool TRACK>
+static cudaError_t launch_fwd(const InfFwdParams& p, cudaStream_t st) {
+    constexpr int BM = 32 * WM, BN = 64 * WN;
+    constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
+    auto kern = inf_fwd_kernel<WM, WN, MODE, TRACK>;
+    static bool configured[64] = {};  // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return e;
+        configured[dev & 63] = true;
+    }
+    dim3 grid((p.B + BM - 1) / BM, (p.CO + BN - 1) / BN);
+    kern<<<grid, WM * WN * 32, SMEM, st>>>(p);
+    return cudaGetLastError();
+}
+
+template <int MODE, bool TRACK>
+static cudaError_t dispatch_dense(const InfFwdParams& p, cudaStream_t st) {
+    const int sms = sm_count();
+    // Largest tile that still gives every SM a CTA; otherwise the smallest.
+    const long t128 = (long)((p.B + 127) / 128) * ((p.CO + 127) / 128);
+    const long t64 = (long)((p.B + 63) / 64) * ((p.CO + 127) / 128);
+    if (t128 >= sms) return launch_fwd<4, 2, MODE, TRACK>(p, st);
+    if (t64 >= sms) return launch_fwd<2, 2, MODE, TRACK>(p, st);
+    return launch_fwd<1, 2, MODE, TRACK>(p, st);
+}
+
+template <bool TRACK>
+static cudaError_t dispatch_fwd(const InfFwdParams& p, cudaStream_t st) {
+    if (p.ci || p.co) {
+        const long t256 = (long)((p.B + 31) / 32) * ((p.CO + 255) / 256);
+        if (t256 >= sm_count()) return launch_fwd<1, 4, MODE_GATHER, TRACK>(p, st);
+        return launch_fwd<1, 2, MODE_GATHER, TRACK>(p, st);
+    }
+    const bool vec = (p.CI % 4 == 0) && (p.W_CI % 4 == 0) && aligned16(p.x) && aligned16(p.w);
+    return vec ? dispatch_dense<MODE_VEC, TRACK>(p, st) : dispatch_dense<MODE_SCALAR, TRACK>(p, st);
+}
+
+cudaError_t inf_forward_values(const float* x, const float* w, float* y, const int* ci, const int* co,
+                               int B, int CO, int CI, int W_CI, cudaStream_t st) {
+    InfFwdParams p{x, w, y, nullptr, ci, co, B, CO, CI, W_CI};
+    return dispatch_fwd<false>(p, st);
+}
+
+}  // namespace snb
+
+using namespace snb;
+
+static int check_fwd(const void* x, const void* w, const void* y, int B, int CO, int CI, int G,
+                     int HW, int W_CO, int W_CI, const int* ci, const int* co) {
+    if (!x || !w || !y) return SNB_ERR_NULL_POINTER;
+    if (G != 1 || HW != 1) return SNB_ERR_UNSUPPORTED;
+    if (B <= 0 || CO <= 0 || CI <= 0 || W_CO <= 0 || W_CI <= 0) return SNB_ERR_BAD_SHAPE;
+    if (!ci && W_CI != CI) return SNB_ERR_BAD_SHAPE;
+    if (!co && W_CO != CO) return SNB_ERR_BAD_SHAPE;
+    if (CI > W_CI || CO > W_CO) return SNB_ERR_BAD_SHAPE;
+    if ((long long)W_CO * W_CI >= (1ll << 31) || (long long)B * CO >= (1ll << 31) ||
+        (long long)B * CI >= (1ll << 31))
+        return SNB_ERR_TOO_LARGE;
+    return SNB_OK;
+}
+
+extern "C" int snb_inf_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G,
+                                    int HW, float* y, int* pos, const int* w_index_ci,
+                                    const int* w_index_co, int W_CO, int W_CI, void* stream) {
+    int rc = check_fwd(x, w, y, B, CO, CI, G, HW, W_CO, W_CI, w_index_ci, w_index_co);
+    if (rc) return rc;
+    if (!pos) return SNB_ERR_NULL_POINTER;
+    if ((CI + CHUNK_TILES * BK - 1) / (CHUNK_TILES * BK) >= 0xffff) return SNB_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    InfFwdParams p{x, w, y, pos, w_index_ci, w_index_co, B, CO, CI, W_CI};
+    SNB_CUDA(dispatch_fwd<true>(p, st));
+    dim3 grid((CO + 31) / 32, (B + 7) / 8);
+    inf_resolve_kernel<<<grid, 256, 0, st>>>(p);
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}
+
+extern "C" int snb_inf_dist_forward_nograd(const float* x, const float* w, int B, int CO, int CI,
+                                           int G, int HW, float* y, void* stream) {
+    int rc = check_fwd(x, w, y, B, CO, CI, G, HW, CO, CI, nullptr, nullptr);
+    if (rc) return rc;
+    InfFwdParams p{x, w, y, nullptr, nullptr, nullptr, B, CO, CI, CI};
+    SNB_CUDA(dispatch_fwd<false>(p, (cudaStream_t)stream));
+    return SNB_OK;
+}
+
+static int inf_backward(const float* g, const int* pos, int B, int CO, int CI, int G, int HW,
+                        float* gx, float* gw, const int* ci, const int* co, int W_CO, int W_CI,
+                        cudaStream_t st) {
+    if (!g || !pos || !gx) return SNB_ERR_NULL_POINTER;
+    if (G != 1 || HW != 1) return SNB_ERR_UNSUPPORTED;
+    if (B <= 0 || CO <= 0 || CI <= 0) return SNB_ERR_BAD_SHAPE;
+    if (gw) {
+        if (W_CO <= 0 || W_CI <= 0 || (!ci && W_CI != CI) || (!co && W_CO != CO)) return SNB_ERR_BAD_SHAPE;
+        if ((long long)W_CO * W_CI >= (1ll << 31)) return SNB_ERR_TOO_LARGE;
+        SNB_CUDA(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)W_CO * W_CI, st));
+    }
+    if ((size_t)CI * sizeof(float) <= 48 * 1024) {
+        inf_bwd_kernel<<<B, 256, CI * sizeof(float), st>>>(g, pos, B, CO, CI, gx, gw, ci, co, W_CI);
+    } else {
+        SNB_CUDA(cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)B * CI, st));
+        dim3 grid((CO + 255) / 256, B);
+        inf_bwd_wide_kernel<<<grid, 256, 0, st>>>(g, pos, B, CO, CI, gx, gw, ci, co, W_CI);
+    }
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}
+
+extern "C" int snb_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO,
+                                           int CI, int G, int HW, float* grad_input, void* stream) {
+    return inf_backward(grad_output, pos, B, CO, CI, G, HW, grad_input, nullptr, nullptr, nullptr,
+                        CO, CI, (cudaStream_t)stream);
+}
+
+extern "C" int snb_inf_dist_backward_input_weight(const float* grad_output, const int* pos, int B,
+                                                  int CO, int CI, int G, int HW, float* grad_input,
+                                                  float* grad_weight, const int* w_index_ci,
+                                                  const int* w_index_co, int W_CO, int W_CI,
+                                                  void* stream) {
+    if (!grad_weight) return SNB_ERR_NULL_POINTER;
+    return inf_backward(grad_output, pos, B, CO, CI, G, HW, grad_input, grad_weight, w_index_ci,
+                        w_index_co, W_CO, W_CI, (cudaStream_t)stream);
+}

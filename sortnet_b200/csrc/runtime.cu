@@ -1,0 +1,41 @@
+// Library-wide host utilities: status strings, last CUDA error, device properties.
+#include "common.cuh"
+#include "launch.h"
+
+namespace snb {
+
+static thread_local cudaError_t g_last = cudaSuccess;
+
+void set_last_cuda_error(cudaError_t e) { g_last = e; }
+
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    int& c = cached[dev & 63];
+    if (c == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        c = v;
+    }
+    return c;
+}
+
+}  // namespace snb
+
+extern "C" const char* snb_status_string(int status) {
+    switch (status) {
+        case SNB_OK: return "ok";
+        case SNB_ERR_NULL_POINTER: return "null pointer argument";
+        case SNB_ERR_BAD_SHAPE: return "inconsistent or non-positive sizes";
+        case SNB_ERR_UNSUPPORTED: return "unsupported configuration (only G = 1, HW = 1, 0 < p)";
+        case SNB_ERR_TOO_LARGE: return "tensor too large for 31-bit indexing";
+        case SNB_ERR_CUDA: return "CUDA runtime error";
+        case SNB_ERR_ALIGNMENT: return "pointer not aligned to its element type";
+        default: return "unknown status";
+    }
+}
+
+extern "C" const char* snb_last_cuda_error(void) { return cudaGetErrorString(snb::g_last); }
+
+extern "C" int snb_version(void) { return 100; }

@@ -1,0 +1,291 @@
+"""Tensor-level entry points with the names and argument order of the reference's
+`norm_dist_cuda` extension module (core/cuda/norm_dist.cpp:294-318).
+
+Every function writes into caller-allocated tensors and returns None, like the reference.
+Differences: work is enqueued on PyTorch's *current* stream of the tensors' device (the
+reference always uses the legacy default stream, forward.cuh:31), the device of the inputs is
+made current for the call, and shapes / dtypes / index ranges that the reference leaves
+unchecked raise RuntimeError instead of corrupting memory.
+
+`install()` registers this module as `norm_dist_cuda` in sys.modules so that the reference's
+unmodified `core/norm_dist.py` (`import norm_dist_cuda as _C`) runs on these kernels.
+"""
+import sys
+
+import torch
+
+from . import _lib
+
+_SUB_BATCH = 32
+
+
+def _check(t, name, dtype=torch.float32):
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+
+
+def _check_opt_index(t, name, n_sub, width):
+    if t is None:
+        return
+    _check(t, name, torch.int32)
+    if t.dim() != 3 or t.size(0) != n_sub or t.size(1) != 1 or t.size(2) != width:
+        raise RuntimeError("%s must have shape [%d, 1, %d], got %s" % (name, n_sub, width, tuple(t.shape)))
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dims(x, out):
+    return x.size(0), out.size(1), x.size(1), x.size(2)
+
+
+def _same_device(*ts):
+    dev = ts[0].device
+    for t in ts[1:]:
+        if t is not None and t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    return dev
+
+
+def inf_dist_forward(input, weight, output, pos, G, w_index_ci=None, w_index_co=None):
+    """core/cuda/norm_dist.cpp:131-147."""
+    _check(input, "input"); _check(weight, "weight"); _check(output, "output")
+    _check(pos, "pos", torch.int32)
+    B, CO, CI, HW = _dims(input, output)
+    S = (B + _SUB_BATCH - 1) // _SUB_BATCH
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI)
+    _check_opt_index(w_index_co, "w_index_co", S, CO)
+    if output.size(0) != B or pos.shape != output.shape:
+        raise RuntimeError("output / pos shape mismatch")
+    dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_inf_dist_forward(
+            _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos),
+            _ptr(w_index_ci), _ptr(w_index_co), weight.size(0), weight.size(1) * G, _stream(input))
+    _lib.check(rc, "inf_dist_forward")
+
+
+def inf_dist_forward_nograd(input, weight, output, G):
+    """core/cuda/norm_dist.cpp:149-156."""
+    _check(input, "input"); _check(weight, "weight"); _check(output, "output")
+    B, CO, CI, HW = _dims(input, output)
+    if weight.size(0) != CO or weight.size(1) * G != CI or output.size(0) != B:
+        raise RuntimeError("shape mismatch between input, weight and output")
+    dev = _same_device(input, weight, output)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_inf_dist_forward_nograd(
+            _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _stream(input))
+    _lib.check(rc, "inf_dist_forward_nograd")
+
+
+def inf_dist_backward_input(grad_output, pos, grad_input, G):
+    """core/cuda/norm_dist.cpp:158-165."""
+    _check(grad_output, "grad_output"); _check(pos, "pos", torch.int32); _check(grad_input, "grad_input")
+    B, CO, CI, HW = grad_output.size(0), grad_output.size(1), grad_input.size(1), grad_input.size(2)
+    if pos.shape != grad_output.shape or grad_input.size(0) != B:
+        raise RuntimeError("shape mismatch between grad_output, pos and grad_input")
+    dev = _same_device(grad_output, pos, grad_input)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_inf_dist_backward_input(
+            _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), _stream(grad_output))
+    _lib.check(rc, "inf_dist_backward_input")
+
+
+def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
+                                   w_index_ci=None, w_index_co=None):
+    """core/cuda/norm_dist.cpp:167-184."""
+    _check(grad_output, "grad_output"); _check(pos, "pos", torch.int32)
+    _check(grad_input, "grad_input"); _check(grad_weight, "grad_weight")
+    B, CO, CI, HW = grad_output.size(0), grad_output.size(1), grad_input.size(1), grad_output.size(2)
+    S = (B + _SUB_BATCH - 1) // _SUB_BATCH
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI)
+    _check_opt_index(w_index_co, "w_index_co", S, CO)
+    if pos.shape != grad_output.shape or grad_input.size(0) != B:
+        raise RuntimeError("shape mismatch between grad_output, pos and grad_input")
+    dev = _same_device(grad_output, pos, grad_input, grad_weight, w_index_ci, w_index_co)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_inf_dist_backward_input_weight(
+            _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), _ptr(grad_weight),
+            _ptr(w_index_ci), _ptr(w_index_co), grad_weight.size(0), grad_weight.size(1) * G,
+            _stream(grad_output))
+    _lib.check(rc, "inf_dist_backward_input_weight")
+
+
+def _lp_common(input, weight, output, w_index_ci, w_index_co):
+    B, CO, CI, HW = _dims(input, output)
+    S = (B + _SUB_BATCH - 1) // _SUB_BATCH
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI)
+    _check_opt_index(w_index_co, "w_index_co", S, CO)
+    return B, CO, CI, HW
+
+
+def norm_dist_forward(input, weight, output, G, p, w_index_ci=None, w_index_co=None):
+    """core/cuda/norm_dist.cpp:43-65 (p <= 10 plain sum, p > 10 max-normalised)."""
+    _check(input, "input"); _check(weight, "weight"); _check(output, "output")
+    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
+    dev = _same_device(input, weight, output, w_index_ci, w_index_co)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_norm_dist_forward(
+            _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), float(p),
+            _ptr(w_index_ci), _ptr(w_index_co), weight.size(0), weight.size(1) * G, _stream(input))
+    _lib.check(rc, "norm_dist_forward")
+
+
+def norm_dist_forward_with_max(input, weight, max_output, output, G, p, w_index_ci=None, w_index_co=None):
+    """core/cuda/norm_dist.cpp:67-85.  Never called by the reference's Python code; provided for
+    completeness.  The supplied maximum is not needed: the result equals norm_dist_forward's."""
+    _check(max_output, "max_output")
+    norm_dist_forward(input, weight, output, G, p, w_index_ci, w_index_co)
+
+
+def norm_dist_backward_input(grad_output, input, weight, output, grad_input, G, p,
+                             w_index_ci=None, w_index_co=None):
+    """core/cuda/norm_dist.cpp:87-106."""
+    for t, n in ((grad_output, "grad_output"), (input, "input"), (weight, "weight"), (output, "output"),
+                 (grad_input, "grad_input")):
+        _check(t, n)
+    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
+    dev = _same_device(grad_output, input, weight, output, grad_input, w_index_ci, w_index_co)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_norm_dist_backward_input(
+            _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW,
+            _ptr(grad_input), float(p), _ptr(w_index_ci), _ptr(w_index_co), weight.size(0),
+            weight.size(1) * G, _stream(input))
+    _lib.check(rc, "norm_dist_backward_input")
+
+
+def norm_dist_backward_input_weight(grad_output, input, weight, output, grad_input, grad_weight, G, p,
+                                    w_index_ci=None, w_index_co=None):
+    """core/cuda/norm_dist.cpp:108-129."""
+    for t, n in ((grad_output, "grad_output"), (input, "input"), (weight, "weight"), (output, "output"),
+                 (grad_input, "grad_input"), (grad_weight, "grad_weight")):
+        _check(t, n)
+    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
+    if grad_weight.shape != weight.shape:
+        raise RuntimeError("grad_weight must have the shape of weight")
+    dev = _same_device(grad_output, input, weight, output, grad_input, grad_weight, w_index_ci, w_index_co)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_norm_dist_backward_input_weight(
+            _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW,
+            _ptr(grad_input), _ptr(grad_weight), float(p), _ptr(w_index_ci), _ptr(w_index_co),
+            weight.size(0), weight.size(1) * G, _stream(input))
+    _lib.check(rc, "norm_dist_backward_input_weight")
+
+
+def bound_inf_dist_forward_nograd(inputL, inputU, weight, outputL, outputU, G):
+    """core/cuda/norm_dist.cpp:186-196."""
+    for t, n in ((inputL, "inputL"), (inputU, "inputU"), (weight, "weight"), (outputL, "outputL"),
+                 (outputU, "outputU")):
+        _check(t, n)
+    B, CO, CI, HW = _dims(inputL, outputL)
+    if inputU.shape != inputL.shape or outputU.shape != outputL.shape or weight.size(0) != CO \
+            or weight.size(1) * G != CI:
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(inputL, inputU, weight, outputL, outputU)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_bound_inf_dist_forward_nograd(
+            _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU),
+            _stream(inputL))
+    _lib.check(rc, "bound_inf_dist_forward_nograd")
+
+
+def bound_inf_dist_forward(inputL, inputU, weight, outputL, outputU, posL, posU, G):
+    """core/cuda/norm_dist.cpp:198-211."""
+    for t, n in ((inputL, "inputL"), (inputU, "inputU"), (weight, "weight"), (outputL, "outputL"),
+                 (outputU, "outputU")):
+        _check(t, n)
+    _check(posL, "posL", torch.int32); _check(posU, "posU", torch.int32)
+    B, CO, CI, HW = _dims(inputL, outputL)
+    if inputU.shape != inputL.shape or outputU.shape != outputL.shape or weight.size(0) != CO \
+            or weight.size(1) * G != CI or posL.shape != outputL.shape or posU.shape != outputL.shape:
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(inputL, inputU, weight, outputL, outputU, posL, posU)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_bound_inf_dist_forward(
+            _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU),
+            _ptr(posL), _ptr(posU), _stream(inputL))
+    _lib.check(rc, "bound_inf_dist_forward")
+
+
+def bound_inf_dist_backward_input(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, G):
+    """core/cuda/norm_dist.cpp:213-226."""
+    for t, n in ((grad_outputL, "grad_outputL"), (grad_outputU, "grad_outputU"),
+                 (grad_inputL, "grad_inputL"), (grad_inputU, "grad_inputU")):
+        _check(t, n)
+    _check(posL, "posL", torch.int32); _check(posU, "posU", torch.int32)
+    B, CO, CI, HW = grad_outputL.size(0), grad_outputL.size(1), grad_inputL.size(1), grad_inputL.size(2)
+    dev = _same_device(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_bound_inf_dist_backward_input(
+            _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
+            _ptr(grad_inputL), _ptr(grad_inputU), _stream(grad_outputL))
+    _lib.check(rc, "bound_inf_dist_backward_input")
+
+
+def bound_inf_dist_backward_input_weight(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU,
+                                         grad_weight, G):
+    """core/cuda/norm_dist.cpp:228-241."""
+    for t, n in ((grad_outputL, "grad_outputL"), (grad_outputU, "grad_outputU"),
+                 (grad_inputL, "grad_inputL"), (grad_inputU, "grad_inputU"), (grad_weight, "grad_weight")):
+        _check(t, n)
+    _check(posL, "posL", torch.int32); _check(posU, "posU", torch.int32)
+    B, CO, CI, HW = grad_outputL.size(0), grad_outputL.size(1), grad_weight.size(1) * G, grad_outputL.size(2)
+    if grad_inputL.size(1) != CI or grad_weight.size(0) != CO:
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, grad_weight)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_bound_inf_dist_backward_input_weight(
+            _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
+            _ptr(grad_inputL), _ptr(grad_inputU), _ptr(grad_weight), _stream(grad_outputL))
+    _lib.check(rc, "bound_inf_dist_backward_input_weight")
+
+
+def mean_shift_stats(x, index, mean, running_mean=None, momentum=0.1):
+    """mean[c] over the rows whose sub-batch kept channel c; optional running-mean update.
+    x [B, C, 1], index [S, 1, C] int32 or None, mean [C_full] (output)."""
+    _check(x, "x"); _check(mean, "mean")
+    B, C = x.size(0), x.size(1)
+    if x.dim() != 3 or x.size(2) != 1:
+        raise RuntimeError("x must have shape [B, C, 1]")
+    S = (B + _SUB_BATCH - 1) // _SUB_BATCH
+    _check_opt_index(index, "index", S, C)
+    if running_mean is not None:
+        _check(running_mean, "running_mean")
+        if running_mean.numel() != mean.numel():
+            raise RuntimeError("running_mean / mean size mismatch")
+    dev = _same_device(x, index, mean, running_mean)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_mean_shift_stats(_ptr(x), _ptr(index), B, C, mean.numel(), _ptr(mean),
+                                              _ptr(running_mean), float(momentum), _stream(x))
+    _lib.check(rc, "mean_shift_stats")
+
+
+def mean_shift_apply(x, mean, index, y):
+    """y[b, j] = x[b, j] - mean[index[s_b][j]]; y may be x."""
+    _check(x, "x"); _check(mean, "mean"); _check(y, "y")
+    B, C = x.size(0), x.size(1)
+    if x.dim() != 3 or x.size(2) != 1 or y.shape != x.shape:
+        raise RuntimeError("x and y must have shape [B, C, 1]")
+    S = (B + _SUB_BATCH - 1) // _SUB_BATCH
+    _check_opt_index(index, "index", S, C)
+    if index is None and mean.numel() != C:
+        raise RuntimeError("mean must have C entries when there is no index")
+    dev = _same_device(x, mean, index, y)
+    with torch.cuda.device(dev):
+        rc = _lib.load().snb_mean_shift_apply(_ptr(x), _ptr(mean), _ptr(index), B, C, _ptr(y), _stream(x))
+    _lib.check(rc, "mean_shift_apply")
+
+
+def install():
+    """Registers this module under the name the reference's operator layer imports."""
+    sys.modules["norm_dist_cuda"] = sys.modules[__name__]
+    return sys.modules[__name__]
