@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the norm-distance hot path on B200: one SortNet-MLP training step plus the
+interval-bound (certification) forward, batch 512 per GPU.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torchrun)
+    python bench.py --impl reference ...                      (the CPU arm, see below)
+
+A step = masked l-inf forward of the 6-layer SortNet-MLP (fresh sub-batch masks), mixture
+loss, sparse backward, gradient all-reduce over NCCL (N > 1), AdamW, then the l-inf interval
+bound forward through all layers under no_grad.  Inputs are seeded synthetic tensors with the
+CIFAR-10 shapes ([512, 3, 32, 32] uniform in [0, 1), labels uniform in [0, 10)), weights
+N(0, 1); the per-GPU batch is fixed as N grows (weak scaling).
+
+Prints one JSON line (rank 0).  `value` is samples/s with inputs resident in HBM; `e2e` is the
+same step fed from pinned host memory with the loss read back every step; `roofline` is the
+dominant kernel's FP32 fraction with the kernel time taken live from CUDA events around its
+launches in the timed region; `cpu_baseline` is the reference's PyTorch way of computing the
+same step, restated in oracle/torch_fallback.py, timed on this host's cores.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = {
+    "name": "SortNet-MLP CIFAR-shaped fwd+bwd+IBP",
+    "input_dim": (3, 32, 32), "depth": 6, "width": 5120, "classes": 10, "keep": 0.9,
+    "batch_per_gpu": 512, "p": float("inf"), "eps_train": 8 / 255, "eps_bound": 8 / 255,
+}
+
+
+def layer_dims():
+    pixels = WORKLOAD["input_dim"][0] * WORKLOAD["input_dim"][1] * WORKLOAD["input_dim"][2]
+    w = WORKLOAD["width"]
+    return [(pixels, w)] + [(w, w)] * (WORKLOAD["depth"] - 2) + [(w, WORKLOAD["classes"])]
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the reference's PyTorch formulation (restated), on a bounded slice of the workload
+# ------------------------------------------------------------------------------------------
+
+def cpu_step_seconds(out_slice, threads):
+    import torch
+    from oracle import torch_fallback
+    torch.set_num_threads(threads)
+    scaled, info = torch_fallback.time_training_slice(
+        layer_dims(), WORKLOAD["keep"], WORKLOAD["p"], WORKLOAD["eps_bound"], out_slice=out_slice, rows=32)
+    return scaled, info
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    out_slice = 128
+    for _ in range(max(args.warmup, 1)):
+        cpu_step_seconds(out_slice, threads)
+    t = []
+    raw = []
+    for _ in range(args.steps):
+        s, info = cpu_step_seconds(out_slice, threads)
+        t.append(s)
+        raw.append(info["raw_seconds"])
+    per32 = statistics.mean(t)
+    value = 32.0 / per32
+    sample = ("32 rows (one sub-batch) x %d of the kept outputs of every wide layer x all inputs, all 6 layers, "
+              "masked l-inf fwd + autograd bwd + dense interval-bound fwd; each part scaled by outputs_full / "
+              "outputs_timed; %.2f s of CPU work per step" % (out_slice, statistics.mean(raw)))
+    line = {
+        "impl": "reference", "metric": "train samples/s (fwd+bwd+IBP step)", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * 512 / value,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_block(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_block(n):
+    return {
+        "workload": "configs[1]: SortNet-MLP (5 x 5120 + head 10), CIFAR-shaped input [512, 3072] per GPU, "
+                    "keep 0.9 sub-batch masks, p = inf, train eps 8/255, IBP eps 8/255",
+        "global_batch": WORKLOAD["batch_per_gpu"] * n, "batch_per_gpu": WORKLOAD["batch_per_gpu"],
+        "parallelism": "dp%d" % n, "optimizer": "AdamW(fused)",
+        "l2": "weights alone are 482 MB per step, larger than the 126 MB L2; no explicit flush",
+    }
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only) every 100 ms."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwPowerBrakeSlowdown: "hw_power_brake",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(0.1)
+
+    def finish(self):
+        self._halt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def mixture_loss(logits, margin, targets, lam=0.1, clip=1.0):
+    import torch.nn.functional as F
+    res = margin.clamp(min=0, max=clip)
+    return res.max(dim=1)[0].mean() + lam * F.cross_entropy(logits, targets)
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from sortnet_b200 import _lib, layers, norm_dist_cuda as C
+    from sortnet_b200.dist import GradientAllReduce, broadcast_parameters
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    B = WORKLOAD["batch_per_gpu"]
+    torch.manual_seed(0)
+    model = layers.SortMLPModel(depth=WORKLOAD["depth"], width=WORKLOAD["width"], input_dim=WORKLOAD["input_dim"],
+                                num_classes=WORKLOAD["classes"], dropout=WORKLOAD["keep"]).to(dev)
+    model.set_p(WORKLOAD["p"])
+    broadcast_parameters(model)
+    torch.manual_seed(1 + rank)  # masks and data differ per rank, like the reference's seed + rank
+    opt = torch.optim.AdamW(model.parameters(), lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, fused=True)
+    sync = GradientAllReduce(model.parameters())
+
+    pool = 4
+    gen = torch.Generator().manual_seed(100 + rank)
+    host_x = [torch.rand(B, *WORKLOAD["input_dim"], generator=gen).pin_memory() for _ in range(pool)]
+    host_t = [torch.randint(0, WORKLOAD["classes"], (B,), generator=gen).pin_memory() for _ in range(pool)]
+    dev_x = [t.to(dev) for t in host_x]
+    dev_t = [t.to(dev) for t in host_t]
+    up = torch.ones(1, device=dev)
+    down = torch.zeros(1, device=dev)
+    eps_t, eps_b = WORKLOAD["eps_train"], WORKLOAD["eps_bound"]
+
+    def step(x, t):
+        model.train()
+        logits, margin = model(x, targets=t, eps=eps_t)
+        loss = mixture_loss(logits, margin, t)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()                                   # per-parameter all-reduces start here
+        with torch.no_grad():                             # certification pass overlaps the exchange
+            cert = model.certified_margin(x, t, eps_b, up, down)
+        sync.finish()
+        opt.step()
+        return loss, cert
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(dev_x[i % pool], dev_t[i % pool])
+    barrier()
+
+    # ---- timed region 1: inputs resident in HBM ------------------------------------------
+    sampler = ClockSampler(local)
+    sampler.start()
+    C.reset_counters()
+    C.start_profile()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(dev_x[i % pool], dev_t[i % pool])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = C.launch_count
+    timeline = C.stop_profile()
+    clocks = sampler.finish()
+
+    # ---- timed region 2: end to end from pinned host memory ------------------------------
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    sink = 0.0
+    for i in range(args.steps):
+        x = host_x[i % pool].to(dev, non_blocking=True)
+        t = host_t[i % pool].to(dev, non_blocking=True)
+        loss, cert = step(x, t)
+        sink += loss.item() + cert.item()                  # device -> host read of the step's results
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3) / args.steps
+
+    times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(times[0]), float(times[1])
+
+    if rank == 0:
+        # FP32 CUDA-core peak of this GPU, measured now (2 flops per FMA)
+        scratch = torch.zeros(4, device=dev)
+        lib = _lib.load()
+        import ctypes
+        flops = ctypes.c_double()
+        best = 0.0
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            _lib.check(lib.snb_probe_fp32(scratch.data_ptr(), 4096, ctypes.byref(flops),
+                                          torch.cuda.current_stream().cuda_stream), "probe_fp32")
+            b.record()
+            torch.cuda.synchronize()
+            best = max(best, flops.value / (a.elapsed_time(b) * 1e-3))
+        peak_gflops = best * 1e-9
+
+        def kernel_stats(entry):
+            rows = {k: v for k, v in timeline.items() if k[0] == entry}
+            if not rows:
+                return None
+            tag = max(rows, key=lambda k: sum(rows[k]))       # the shape that took the most time
+            return tag[1], statistics.mean(rows[tag]), sum(sum(v) for v in rows.values())
+
+        by_entry = {}
+        for (entry, tag), v in timeline.items():
+            by_entry[entry] = by_entry.get(entry, 0.0) + sum(v)
+        total_kernel_ms = sum(by_entry.values())
+        shares = {k[4:]: round(v / total_kernel_ms, 4) for k, v in sorted(by_entry.items(), key=lambda kv: -kv[1])}
+
+        roofs = {}
+        for entry, ops_per_elem in (("snb_bound_inf_dist_forward_nograd", 6.0), ("snb_inf_dist_forward", 2.0)):
+            ks = kernel_stats(entry)
+            if ks is None:
+                continue
+            (b_, co_, ci_), mean_ms, _ = ks
+            achieved = ops_per_elem * b_ * co_ * ci_ / (mean_ms * 1e-3) * 1e-9
+            roofs[entry] = {
+                "bound": "fp32", "kernel": entry[4:], "shape_B_CO_CI": [b_, co_, ci_],
+                "ops_per_element": ops_per_elem, "ms_per_launch": round(mean_ms, 4),
+                "achieved": round(achieved, 1), "peak": round(peak_gflops, 1), "unit": "GFLOP/s",
+                "frac": round(achieved / peak_gflops, 4), "traffic": None,
+                "peak_source": "FFMA probe timed in this run (2 flops per FMA); MEASURED_PEAKS.json has no FP32 "
+                               "figure; nominal 148 SM x 128 lanes x 2 x 1.965 GHz = 74.5 TFLOP/s",
+            }
+        dominant = max(roofs.values(), key=lambda r: by_entry.get("snb_" + r["kernel"], 0.0)) if roofs else None
+
+        value = world * B / (ms * 1e-3)
+        e2e = world * B / (ms_e2e * 1e-3)
+        h2d = sum(t.numel() * t.element_size() for t in (host_x[0], host_t[0]))
+        line = {
+            "metric": "train samples/s (fwd+bwd+IBP step)", "value": round(value, 1), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_block(world),
+            "e2e": {"value": round(e2e, 1), "unit": "samples/s", "ms_per_step": round(ms_e2e, 3),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": dominant,
+            "roofline_linf_forward": roofs.get("snb_inf_dist_forward"),
+            "kernel_time_share": shares,
+            "kernel_ms_per_step": round(total_kernel_ms / args.steps, 3),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            cpu_step_seconds(64, threads)                      # warm-up
+            scaled, info = cpu_step_seconds(256, threads)
+            line["cpu_baseline"] = {
+                "value": round(32.0 / scaled, 4), "unit": "samples/s", "cores": threads, "kind": "port",
+                "sample": "32 rows x 256 outputs of every wide layer x all inputs, all 6 layers, masked l-inf "
+                          "fwd + autograd bwd + dense interval-bound fwd in PyTorch on the host (%.1f s), each "
+                          "part scaled by outputs_full / outputs_timed" % info["raw_seconds"],
+            }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -44,6 +44,11 @@ const char* snb_status_string(int status);
 const char* snb_last_cuda_error(void);
 int snb_version(void);
 
+/* Runs a register-only FMA chain (no counterpart in the reference); *flops = operations done.
+ * The benchmark times it to get the FP32 CUDA-core peak used in its roofline fractions.
+ * scratch: at least 4 bytes of device memory. */
+int snb_probe_fp32(float* scratch, int iters, double* flops, void* stream);
+
 /* ---- l-infinity distance ---------------------------------------------------------------- */
 
 /* y[b,j] = max(1e-10, max_c |x[b,c] - w[co[s][j], ci[s][c]]|), pos[b,j] = lowest such c, bit 31

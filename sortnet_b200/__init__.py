@@ -6,8 +6,9 @@ Layout
     _lib.py               ctypes loader for the C ABI
     norm_dist_cuda.py     tensor-level functions with the names and argument order of the
                           reference's `norm_dist_cuda` extension module
-    norm_dist.py          operator / autograd layer with the signatures of core/norm_dist.py
+    ops.py                operator / autograd layer with the signatures of core/norm_dist.py
+    layers.py             NormDist / MeanShiftDropout modules and the SortNet-MLP harness
 
 There is no CPU implementation: every operator raises if the CUDA library cannot be loaded.
 """
-__all__ = ["norm_dist_cuda", "norm_dist"]
+__all__ = ["norm_dist_cuda", "ops", "layers"]

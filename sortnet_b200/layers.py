@@ -1,0 +1,264 @@
+"""Layers around the operators: mask sampling, the mean-shift module, the norm-distance
+layer and a SortNet-MLP built from them.
+
+What is mirrored from the reference
+    sample_mask          core/models/norm_dist.py:14-17   (same index-list format)
+    MeanShiftDropout     core/models/bound_basic_module.py:107-160  (forward signature, buffer name
+                         `running_mean`, momentum rule, gradient through the batch mean)
+    NormDist             core/models/norm_dist.py:20-121  (parameters `weight` [CO, CI], `bias`;
+                         std / identity initialisation; attribute `p`; returns the triple
+                         (x, lower, upper))
+    SortMLPModel         ell_inf_models.py:17-50           (layer stack, forward signature, margin)
+so a reference checkpoint's state_dict loads into SortMLPModel unchanged.
+
+What is designed differently: the reference threads the sub-batch masks from one layer to the
+next through class-level globals (NormDistBase.dropout_list / dropout_buffer); here the model
+owns its layers and hands each one the masks explicitly, and mean-shift runs in two small
+deterministic kernels instead of a dozen PyTorch launches.
+"""
+import math
+
+import torch
+import torch.nn as nn
+
+from . import norm_dist_cuda as _C
+from . import ops
+
+SUB_BATCH = 32
+
+
+def sample_mask(batch, groups, channel, q, device):
+    """Kept-channel lists for `batch` sub-batches: one Binomial(channel, q) count shared by all
+    sub-batches, a uniformly random subset of that size per (sub-batch, group), sorted, int32,
+    shape [batch, groups, count]."""
+    count = int((torch.rand(channel, device=device) < q).sum().item())
+    scores = torch.rand(batch, groups, channel, device=device)
+    picked = torch.topk(scores, k=count, dim=-1, sorted=False)[1].int()
+    return torch.sort(picked)[0]
+
+
+def _as_index32(index):
+    if index is None:
+        return None
+    if index.dtype != torch.int32:
+        index = index.int()
+    return index.contiguous()
+
+
+class _MeanShiftTrainF(torch.autograd.Function):
+    """y = x - mean(x) with the mean taken over the rows whose sub-batch kept the channel.
+    The backward applies the same centring to the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, x, index, running_mean, momentum):
+        x = x.contiguous()
+        mean = torch.empty(running_mean.numel(), device=x.device, dtype=torch.float32)
+        _C.mean_shift_stats(x, index, mean, running_mean, momentum)
+        y = torch.empty_like(x)
+        _C.mean_shift_apply(x, mean, index, y)
+        ctx.index = index
+        ctx.channels = running_mean.numel()
+        ctx.mark_non_differentiable(mean)
+        return y, mean
+
+    @staticmethod
+    def backward(ctx, grad_y, _grad_mean):
+        grad_y = grad_y.contiguous()
+        gmean = torch.empty(ctx.channels, device=grad_y.device, dtype=torch.float32)
+        _C.mean_shift_stats(grad_y, ctx.index, gmean, None, 0.0)
+        grad_x = torch.empty_like(grad_y)
+        _C.mean_shift_apply(grad_y, gmean, ctx.index, grad_x)
+        return grad_x, None, None, None
+
+
+class MeanShiftDropout(nn.Module):
+    """Subtracts the per-channel batch mean (training) or the running mean (evaluation)."""
+
+    def __init__(self, out_channels, momentum=0.1, affine=True):
+        super().__init__()
+        self.out_channels = out_channels
+        self.momentum = momentum
+        self.affine = affine
+        self.register_buffer("running_mean", torch.zeros(out_channels))
+        if affine:
+            self.bias = nn.Parameter(torch.zeros(out_channels))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x=None, lower=None, upper=None, index=None):
+        """x, lower, upper: (B, C, 1) or None; index: kept channels [S, 1, C] or None."""
+        index = _as_index32(index)
+        if self.training:
+            assert x is not None, "training needs the activations"
+            x, mean = _MeanShiftTrainF.apply(x, index, self.running_mean, self.momentum)
+            if self.bias is not None:
+                x = x + self._gathered(self.bias, index, x.size(0)).unsqueeze(-1)
+                mean = mean - self.bias.detach()
+            x_done, todo = x, (None, lower, upper)
+        else:
+            mean = self.running_mean if self.bias is None else self.running_mean - self.bias.detach()
+            x_done, todo = None, (x, lower, upper)
+        outs = []
+        for z in todo:
+            if z is None:
+                outs.append(None)
+                continue
+            z = z.contiguous()
+            out = torch.empty_like(z)
+            _C.mean_shift_apply(z, mean, index, out)
+            outs.append(out)
+        if x_done is not None:
+            outs[0] = x_done
+        return tuple(outs)
+
+    @staticmethod
+    def _gathered(vec, index, batch):
+        if index is None:
+            return vec.unsqueeze(0)
+        rows = torch.arange(batch, device=vec.device) // SUB_BATCH
+        return vec[index[rows, 0].long()]
+
+    def extra_repr(self):
+        return "{}, affine={}".format(self.out_channels, self.affine)
+
+
+class NormDist(nn.Module):
+    """Fully connected norm-distance layer y_j = ||x - w_j||_p (+ mean shift, + bias).
+
+    `dropout` is the *keep* rate q of the sort neuron this layer estimates during training
+    (None or 1.0 = plain l-p / l-inf distance).  Inputs and outputs are 2-D (B, C)."""
+
+    def __init__(self, in_features, out_features, p=float("inf"), bias=True, std=1.0, mean_shift=True,
+                 dropout=None, identity_val=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.p = p
+        self.dropout = dropout
+        self.weight = nn.Parameter(torch.randn(out_features, in_features) * std)
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self.mean_shift = MeanShiftDropout(out_features, affine=False) if mean_shift else None
+        if identity_val is not None and in_features <= out_features:
+            with torch.no_grad():
+                rows = torch.arange(out_features)
+                self.weight[rows, rows % in_features] = -identity_val
+
+    @property
+    def keep_rate(self):
+        return 1.0 if self.dropout is None else self.dropout
+
+    def forward(self, x=None, lower=None, upper=None, mask_in=None, mask_out=None, sort_eval=False):
+        """With masks (training): x is compact over `mask_in`, the result compact over `mask_out`.
+        Without masks: the l-p / l-inf distance of the point value and, when a box
+        (lower, upper) is given, its interval bounds (p must be inf).  `sort_eval=True` replaces
+        the distance by the deterministic sort neuron with q = `dropout` (the expectation of
+        the masked training-time neuron), as the reference does outside training."""
+        masked = mask_in is not None or mask_out is not None
+        x3, l3, u3 = (None if z is None else z.unsqueeze(-1).contiguous() for z in (x, lower, upper))
+        if masked:
+            x3 = ops.norm_dist_dropout(x3, self.weight, mask_in, mask_out, self.p)
+        elif not sort_eval:
+            if x3 is not None:
+                x3 = ops.norm_dist(x3, self.weight, self.p)
+            if l3 is not None and u3 is not None:
+                assert math.isinf(self.p)
+                l3, u3 = ops.bound_inf_dist(l3, u3, self.weight)
+        else:
+            x3 = ops.sort_neuron(x3, self.weight, q=self.dropout)
+            if l3 is not None and u3 is not None:
+                l3, u3 = ops.bound_sort_neuron(l3, u3, self.weight, q=self.dropout)
+        if self.mean_shift is not None:
+            x3, l3, u3 = self.mean_shift(x3, l3, u3, index=mask_out)
+        if self.bias is not None:
+            b = MeanShiftDropout._gathered(self.bias, mask_out, x3.size(0) if x3 is not None else l3.size(0))
+            x3, l3, u3 = (None if z is None else z + b.unsqueeze(-1) for z in (x3, l3, u3))
+        return tuple(None if z is None else z.squeeze(-1) for z in (x3, l3, u3))
+
+    def extra_repr(self):
+        return "in_features={}, out_features={}, bias={}, keep={}".format(
+            self.in_features, self.out_features, self.bias is not None, self.dropout)
+
+
+class SortMLPModel(nn.Module):
+    """depth norm-distance layers: pixels -> width -> ... -> width -> num_classes.
+
+    Layers 2..depth estimate the sort neuron with keep rate `dropout` on their inputs, so the
+    outputs of layers 1..depth-1 are sub-sampled; the head has a bias and no mean shift."""
+
+    def __init__(self, depth, width, input_dim, num_classes=10, dropout=0.7, std=1.0, identity_val=None,
+                 scalar=False):
+        super().__init__()
+        pixels = input_dim[0] * input_dim[1] * input_dim[2]
+        kw = dict(std=std, identity_val=identity_val)
+        layers = [NormDist(pixels, width, bias=False, mean_shift=True, **kw)]
+        for _ in range(depth - 2):
+            layers.append(NormDist(width, width, bias=False, mean_shift=True, dropout=dropout, **kw))
+        layers.append(NormDist(width, num_classes, bias=True, mean_shift=False, dropout=dropout, **kw))
+        self.fc_dist = nn.ModuleList(layers)
+        if isinstance(scalar, float):
+            self.scalar = scalar
+        else:
+            self.scalar = nn.Parameter(torch.ones(1)) if scalar else 1
+
+    def set_p(self, p):
+        for layer in self.fc_dist:
+            layer.p = p
+
+    def _certifying(self):
+        return all(math.isinf(l.p) and not l.training for l in self.fc_dist)
+
+    def draw_masks(self, batch, device):
+        """One kept-channel list per hidden activation (None where the next layer keeps all)."""
+        sub = (batch - 1) // SUB_BATCH + 1
+        masks = []
+        for nxt in self.fc_dist[1:]:
+            q = nxt.keep_rate
+            masks.append(None if q == 1.0 else sample_mask(sub, 1, nxt.in_features, q, device))
+        return masks
+
+    @torch.no_grad()
+    def certified_margin(self, x, targets, eps, up, down):
+        """Evaluation-mode l-inf interval-bound pass over the box [x - eps, x + eps] clipped to
+        [down, up]: every layer propagates the point value and the bounds with the plain
+        l-inf distance (keep rate 1), running means are subtracted.  Returns the fraction of
+        rows whose worst-case margin is negative for every wrong class (certified accuracy)."""
+        was_training = self.training
+        self.eval()
+        try:
+            x = x.reshape(x.size(0), -1)
+            lower = torch.maximum(x - eps, down)
+            upper = torch.minimum(x + eps, up)
+            for layer in self.fc_dist:
+                assert math.isinf(layer.p)
+                x, lower, upper = layer(x, lower, upper, sort_eval=False)
+            score_lo, score_hi = -upper, -lower
+            margin = score_hi - torch.gather(score_lo, 1, targets.view(-1, 1))
+            margin = margin.scatter(1, targets.view(-1, 1), float("-inf"))
+            return (margin.max(dim=1)[0] < 0).float().mean()
+        finally:
+            self.train(was_training)
+
+    def forward(self, x=None, targets=None, eps=0, up=None, down=None, masks=None):
+        x = x.reshape(x.size(0), -1)
+        lower = upper = None
+        if up is not None and down is not None and self._certifying():
+            lower = torch.maximum(x - eps, down.reshape(1, -1) if down.dim() else down)
+            upper = torch.minimum(x + eps, up.reshape(1, -1) if up.dim() else up)
+        has_dropout = any(l.keep_rate != 1.0 for l in self.fc_dist)
+        use_masks = has_dropout and self.training and torch.is_grad_enabled()
+        if use_masks and masks is None:
+            masks = self.draw_masks(x.size(0), x.device)
+        mask_in = None
+        for k, layer in enumerate(self.fc_dist):
+            mask_out = masks[k] if (use_masks and k < len(masks)) else None
+            x, lower, upper = layer(x, lower, upper, mask_in=mask_in, mask_out=mask_out,
+                                    sort_eval=has_dropout and not use_masks)
+            mask_in = mask_out
+        if targets is None:
+            return -x * self.scalar
+        lo = x - eps if lower is None else lower
+        hi = x + eps if upper is None else upper
+        # distances -> scores: negate, so the roles of the bounds swap
+        score, score_lo, score_hi = -x, -hi, -lo
+        margin = score_hi - torch.gather(score_lo, 1, targets.view(-1, 1))
+        margin = margin.scatter(1, targets.view(-1, 1), 0)
+        return score * self.scalar, margin / (2 * eps)

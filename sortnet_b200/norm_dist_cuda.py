@@ -40,12 +40,63 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def _stream(t):
-    return torch.cuda.current_stream(t.device).cuda_stream
-
-
 def _dims(x, out):
     return x.size(0), out.size(1), x.size(1), x.size(2)
+
+
+# Kernels launched by each C entry point (memsets are not counted).
+_KERNELS = {
+    "snb_inf_dist_forward": 2, "snb_inf_dist_forward_nograd": 1, "snb_inf_dist_backward_input": 1,
+    "snb_inf_dist_backward_input_weight": 1, "snb_norm_dist_forward": 1, "snb_norm_dist_backward_input": 1,
+    "snb_norm_dist_backward_input_weight": 1, "snb_bound_inf_dist_forward_nograd": 1,
+    "snb_bound_inf_dist_forward": 1, "snb_bound_inf_dist_backward_input": 1,
+    "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1,
+}
+
+launch_count = 0          # kernels launched through this module since import / reset_counters()
+_timeline = None          # when profiling: list of (entry point, work tag, start event, end event)
+
+
+def reset_counters():
+    global launch_count
+    launch_count = 0
+
+
+def start_profile():
+    """Record a CUDA event pair around every entry-point call (on the stream it launches on)."""
+    global _timeline
+    _timeline = []
+
+
+def stop_profile():
+    """Returns {(entry point, work tag): [milliseconds per call]}; synchronises the device."""
+    global _timeline
+    tl, _timeline = _timeline or [], None
+    torch.cuda.synchronize()
+    out = {}
+    for name, tag, e0, e1 in tl:
+        out.setdefault((name, tag), []).append(e0.elapsed_time(e1))
+    return out
+
+
+def _call(dev, ref_tensor, entry, tag, *args):
+    """Runs C entry point `entry` with `dev` current, on the current stream of that device."""
+    global launch_count
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev)
+        if _timeline is not None:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        rc = getattr(lib, entry)(*args, stream.cuda_stream)
+        if _timeline is not None:
+            e1.record(stream)
+            _timeline.append((entry, tag, e0, e1))
+    _lib.check(rc, entry[4:])
+    launch_count += _KERNELS[entry]
+    if entry == "snb_norm_dist_forward" and args[8] > 10.0:
+        launch_count += 1      # the l-inf pass that supplies the normaliser
 
 
 def _same_device(*ts):
@@ -67,11 +118,9 @@ def inf_dist_forward(input, weight, output, pos, G, w_index_ci=None, w_index_co=
     if output.size(0) != B or pos.shape != output.shape:
         raise RuntimeError("output / pos shape mismatch")
     dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_inf_dist_forward(
-            _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos),
-            _ptr(w_index_ci), _ptr(w_index_co), weight.size(0), weight.size(1) * G, _stream(input))
-    _lib.check(rc, "inf_dist_forward")
+    _call(dev, input, "snb_inf_dist_forward", (B, CO, CI),
+          _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos), _ptr(w_index_ci),
+          _ptr(w_index_co), weight.size(0), weight.size(1) * G)
 
 
 def inf_dist_forward_nograd(input, weight, output, G):
@@ -81,10 +130,8 @@ def inf_dist_forward_nograd(input, weight, output, G):
     if weight.size(0) != CO or weight.size(1) * G != CI or output.size(0) != B:
         raise RuntimeError("shape mismatch between input, weight and output")
     dev = _same_device(input, weight, output)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_inf_dist_forward_nograd(
-            _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _stream(input))
-    _lib.check(rc, "inf_dist_forward_nograd")
+    _call(dev, input, "snb_inf_dist_forward_nograd", (B, CO, CI),
+          _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output))
 
 
 def inf_dist_backward_input(grad_output, pos, grad_input, G):
@@ -94,10 +141,8 @@ def inf_dist_backward_input(grad_output, pos, grad_input, G):
     if pos.shape != grad_output.shape or grad_input.size(0) != B:
         raise RuntimeError("shape mismatch between grad_output, pos and grad_input")
     dev = _same_device(grad_output, pos, grad_input)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_inf_dist_backward_input(
-            _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), _stream(grad_output))
-    _lib.check(rc, "inf_dist_backward_input")
+    _call(dev, grad_output, "snb_inf_dist_backward_input", (B, CO, CI),
+          _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input))
 
 
 def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
@@ -112,12 +157,9 @@ def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
     if pos.shape != grad_output.shape or grad_input.size(0) != B:
         raise RuntimeError("shape mismatch between grad_output, pos and grad_input")
     dev = _same_device(grad_output, pos, grad_input, grad_weight, w_index_ci, w_index_co)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_inf_dist_backward_input_weight(
-            _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), _ptr(grad_weight),
-            _ptr(w_index_ci), _ptr(w_index_co), grad_weight.size(0), grad_weight.size(1) * G,
-            _stream(grad_output))
-    _lib.check(rc, "inf_dist_backward_input_weight")
+    _call(dev, grad_output, "snb_inf_dist_backward_input_weight", (B, CO, CI),
+          _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), _ptr(grad_weight),
+          _ptr(w_index_ci), _ptr(w_index_co), grad_weight.size(0), grad_weight.size(1) * G)
 
 
 def _lp_common(input, weight, output, w_index_ci, w_index_co):
@@ -133,11 +175,9 @@ def norm_dist_forward(input, weight, output, G, p, w_index_ci=None, w_index_co=N
     _check(input, "input"); _check(weight, "weight"); _check(output, "output")
     B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
     dev = _same_device(input, weight, output, w_index_ci, w_index_co)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_norm_dist_forward(
-            _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), float(p),
-            _ptr(w_index_ci), _ptr(w_index_co), weight.size(0), weight.size(1) * G, _stream(input))
-    _lib.check(rc, "norm_dist_forward")
+    _call(dev, input, "snb_norm_dist_forward", (B, CO, CI),
+          _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), float(p), _ptr(w_index_ci),
+          _ptr(w_index_co), weight.size(0), weight.size(1) * G)
 
 
 def norm_dist_forward_with_max(input, weight, max_output, output, G, p, w_index_ci=None, w_index_co=None):
@@ -155,12 +195,9 @@ def norm_dist_backward_input(grad_output, input, weight, output, grad_input, G, 
         _check(t, n)
     B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
     dev = _same_device(grad_output, input, weight, output, grad_input, w_index_ci, w_index_co)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_norm_dist_backward_input(
-            _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW,
-            _ptr(grad_input), float(p), _ptr(w_index_ci), _ptr(w_index_co), weight.size(0),
-            weight.size(1) * G, _stream(input))
-    _lib.check(rc, "norm_dist_backward_input")
+    _call(dev, input, "snb_norm_dist_backward_input", (B, CO, CI),
+          _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW, _ptr(grad_input),
+          float(p), _ptr(w_index_ci), _ptr(w_index_co), weight.size(0), weight.size(1) * G)
 
 
 def norm_dist_backward_input_weight(grad_output, input, weight, output, grad_input, grad_weight, G, p,
@@ -173,12 +210,10 @@ def norm_dist_backward_input_weight(grad_output, input, weight, output, grad_inp
     if grad_weight.shape != weight.shape:
         raise RuntimeError("grad_weight must have the shape of weight")
     dev = _same_device(grad_output, input, weight, output, grad_input, grad_weight, w_index_ci, w_index_co)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_norm_dist_backward_input_weight(
-            _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW,
-            _ptr(grad_input), _ptr(grad_weight), float(p), _ptr(w_index_ci), _ptr(w_index_co),
-            weight.size(0), weight.size(1) * G, _stream(input))
-    _lib.check(rc, "norm_dist_backward_input_weight")
+    _call(dev, input, "snb_norm_dist_backward_input_weight", (B, CO, CI),
+          _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW, _ptr(grad_input),
+          _ptr(grad_weight), float(p), _ptr(w_index_ci), _ptr(w_index_co), weight.size(0),
+          weight.size(1) * G)
 
 
 def bound_inf_dist_forward_nograd(inputL, inputU, weight, outputL, outputU, G):
@@ -191,11 +226,8 @@ def bound_inf_dist_forward_nograd(inputL, inputU, weight, outputL, outputU, G):
             or weight.size(1) * G != CI:
         raise RuntimeError("shape mismatch")
     dev = _same_device(inputL, inputU, weight, outputL, outputU)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_bound_inf_dist_forward_nograd(
-            _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU),
-            _stream(inputL))
-    _lib.check(rc, "bound_inf_dist_forward_nograd")
+    _call(dev, inputL, "snb_bound_inf_dist_forward_nograd", (B, CO, CI),
+          _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU))
 
 
 def bound_inf_dist_forward(inputL, inputU, weight, outputL, outputU, posL, posU, G):
@@ -209,11 +241,9 @@ def bound_inf_dist_forward(inputL, inputU, weight, outputL, outputU, posL, posU,
             or weight.size(1) * G != CI or posL.shape != outputL.shape or posU.shape != outputL.shape:
         raise RuntimeError("shape mismatch")
     dev = _same_device(inputL, inputU, weight, outputL, outputU, posL, posU)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_bound_inf_dist_forward(
-            _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU),
-            _ptr(posL), _ptr(posU), _stream(inputL))
-    _lib.check(rc, "bound_inf_dist_forward")
+    _call(dev, inputL, "snb_bound_inf_dist_forward", (B, CO, CI),
+          _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU),
+          _ptr(posL), _ptr(posU))
 
 
 def bound_inf_dist_backward_input(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, G):
@@ -224,11 +254,9 @@ def bound_inf_dist_backward_input(grad_outputL, grad_outputU, posL, posU, grad_i
     _check(posL, "posL", torch.int32); _check(posU, "posU", torch.int32)
     B, CO, CI, HW = grad_outputL.size(0), grad_outputL.size(1), grad_inputL.size(1), grad_inputL.size(2)
     dev = _same_device(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_bound_inf_dist_backward_input(
-            _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
-            _ptr(grad_inputL), _ptr(grad_inputU), _stream(grad_outputL))
-    _lib.check(rc, "bound_inf_dist_backward_input")
+    _call(dev, grad_outputL, "snb_bound_inf_dist_backward_input", (B, CO, CI),
+          _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
+          _ptr(grad_inputL), _ptr(grad_inputU))
 
 
 def bound_inf_dist_backward_input_weight(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU,
@@ -242,11 +270,9 @@ def bound_inf_dist_backward_input_weight(grad_outputL, grad_outputU, posL, posU,
     if grad_inputL.size(1) != CI or grad_weight.size(0) != CO:
         raise RuntimeError("shape mismatch")
     dev = _same_device(grad_outputL, grad_outputU, posL, posU, grad_inputL, grad_inputU, grad_weight)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_bound_inf_dist_backward_input_weight(
-            _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
-            _ptr(grad_inputL), _ptr(grad_inputU), _ptr(grad_weight), _stream(grad_outputL))
-    _lib.check(rc, "bound_inf_dist_backward_input_weight")
+    _call(dev, grad_outputL, "snb_bound_inf_dist_backward_input_weight", (B, CO, CI),
+          _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
+          _ptr(grad_inputL), _ptr(grad_inputU), _ptr(grad_weight))
 
 
 def mean_shift_stats(x, index, mean, running_mean=None, momentum=0.1):
@@ -263,10 +289,8 @@ def mean_shift_stats(x, index, mean, running_mean=None, momentum=0.1):
         if running_mean.numel() != mean.numel():
             raise RuntimeError("running_mean / mean size mismatch")
     dev = _same_device(x, index, mean, running_mean)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_mean_shift_stats(_ptr(x), _ptr(index), B, C, mean.numel(), _ptr(mean),
-                                              _ptr(running_mean), float(momentum), _stream(x))
-    _lib.check(rc, "mean_shift_stats")
+    _call(dev, x, "snb_mean_shift_stats", (B, C),
+          _ptr(x), _ptr(index), B, C, mean.numel(), _ptr(mean), _ptr(running_mean), float(momentum))
 
 
 def mean_shift_apply(x, mean, index, y):
@@ -280,9 +304,8 @@ def mean_shift_apply(x, mean, index, y):
     if index is None and mean.numel() != C:
         raise RuntimeError("mean must have C entries when there is no index")
     dev = _same_device(x, mean, index, y)
-    with torch.cuda.device(dev):
-        rc = _lib.load().snb_mean_shift_apply(_ptr(x), _ptr(mean), _ptr(index), B, C, _ptr(y), _stream(x))
-    _lib.check(rc, "mean_shift_apply")
+    _call(dev, x, "snb_mean_shift_apply", (B, C),
+          _ptr(x), _ptr(mean), _ptr(index), B, C, _ptr(y))
 
 
 def install():

@@ -3,7 +3,7 @@
 Run once, in a container that has the reference checkout (path in $SORTNET_REFERENCE,
 default /root/reference):   python tests/golden/make_golden.py
 
-The reference's pure-PyTorch branches are imported unmodified with an empty stand-in for
+The reference's pure-PyTorch branches are imported unmodified with a CPU stand-in for
 its CUDA extension module, evaluated on CPU on small seeded inputs, and their outputs and
 autograd gradients are stored as .npz files.  The tests then check the CPU oracle (and,
 through it, the CUDA kernels) against these files; nothing at test time reads the
@@ -15,9 +15,9 @@ inner norm_dist call forced onto the PyTorch branch), :224-230 (sort_neuron), :2
 core/models/norm_dist.py:14-17 (sample_mask).
 """
 import functools
+import math
 import os
 import sys
-import types
 
 import numpy as np
 import torch
@@ -25,7 +25,13 @@ import torch
 REF = os.environ.get("SORTNET_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-sys.modules["norm_dist_cuda"] = types.ModuleType("norm_dist_cuda")
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+from oracle import ref_module  # noqa: E402
+
+# Stand-in for the reference's CUDA extension: the PyTorch branches never call it; the
+# model-level case runs the reference's autograd Functions on it (oracle/ref_module.py).
+ref_module.install()
 sys.path.insert(0, REF)
 import core.norm_dist as ref_ops  # noqa: E402
 from core.models.bound_basic_module import MeanShiftDropout  # noqa: E402
@@ -144,6 +150,51 @@ def case_mean_shift(seed, B, C_full, q):
     return out
 
 
+def case_model(seed, B, depth, width, input_dim, classes, q, p, eps):
+    """The reference's unmodified SortMLPModel on CPU, with its CUDA extension replaced by the
+    oracle-backed stand-in (oracle/ref_module.py) and its mask sampler fed fixed masks."""
+    import ell_inf_models
+    ref_layers = sys.modules["core.models.norm_dist"]
+    ref_layers.NormDistBase.dropout_list = dict()
+    ref_layers.NormDistBase.dropout_buffer = None
+    ref_layers.NormDistBase.tag = 0
+    torch.manual_seed(seed)
+    model = ell_inf_models.SortMLPModel(depth=depth, width=width, input_dim=input_dim,
+                                        num_classes=classes, dropout=q)
+    for m in model.modules():
+        if isinstance(m, ref_layers.NormDistBase):
+            m.p = p
+    S = (B - 1) // 32 + 1
+    masks = [sample_mask(S, 1, width, q, device="cpu") for _ in range(depth - 1)]
+    feed = iter(masks)
+    ref_layers.sample_mask = lambda *a, **k: next(feed)
+    x = torch.rand(B, *input_dim)
+    targets = torch.randint(0, classes, (B,))
+    out = {"x": x.reshape(B, -1), "targets": targets, "p": np.float64(p), "eps": np.float64(eps),
+           "q": np.float64(q)}
+    for i, mk in enumerate(masks):
+        out["mask%d" % i] = mk[:, 0]
+    state0 = {k: v.clone() for k, v in model.state_dict().items()}
+    model.train()
+    logits, margin = model(x, targets=targets, eps=eps)
+    loss = margin.clamp(min=0).max(dim=1)[0].mean() + 0.5 * torch.nn.functional.cross_entropy(logits, targets)
+    loss.backward()
+    out.update(logits=logits.detach(), margin=margin.detach(), loss=loss.detach())
+    for k, v in state0.items():
+        out["state0." + k] = v
+    for k, v in model.state_dict().items():
+        if "running_mean" in k:
+            out["state1." + k] = v
+    for k, prm in model.named_parameters():
+        out["grad." + k] = prm.grad
+    if q == 1.0 and math.isinf(p):
+        model.eval()
+        with torch.no_grad():
+            lg, mg = model(x, targets=targets, eps=eps, up=torch.ones(1), down=torch.zeros(1))
+        out.update(eval_logits=lg, eval_margin=mg)
+    return out
+
+
 def save(name, d):
     arrs = {k: (v.detach().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in d.items()}
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrs)
@@ -166,6 +217,9 @@ def main():
     save("sort_a", case_sort(30, 20, 48, 12, 0.6, 10))
     save("mean_shift_masked", case_mean_shift(40, 70, 40, 0.8))
     save("mean_shift_plain", case_mean_shift(41, 45, 24, None))
+    save("model_inf_masked", case_model(50, 70, 4, 96, (3, 4, 4), 10, 0.8, INF, 0.03))
+    save("model_p8_masked", case_model(51, 70, 4, 96, (3, 4, 4), 10, 0.8, 8.0, 0.03))
+    save("model_inf_plain", case_model(52, 45, 3, 64, (3, 4, 4), 10, 1.0, INF, 0.03))
 
 
 if __name__ == "__main__":
