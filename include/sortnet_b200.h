@@ -49,6 +49,11 @@ int snb_version(void);
  * scratch: at least 4 bytes of device memory. */
 int snb_probe_fp32(float* scratch, int iters, double* flops, void* stream);
 
+/* Runs a register-only loop of the max-plus inner step in instruction form `variant` (0..6; no
+ * counterpart in the reference); *pairs = output-pairs processed, each two reduction steps.
+ * scratch: at least 2 * SMs * 256 + 64 floats of device memory, first 64 read as operands. */
+int snb_probe_step(int variant, float* scratch, int iters, double* pairs, void* stream);
+
 /* ---- l-infinity distance ---------------------------------------------------------------- */
 
 /* y[b,j] = max(1e-10, max_c |x[b,c] - w[co[s][j], ci[s][c]]|), pos[b,j] = lowest such c, bit 31

@@ -9,7 +9,7 @@
 // Forward = max-plus "GEMM": 8x8 outputs per thread, two reduction steps per instruction pair
 // (packed fp32 subtract on a register pair + three-input |.|-max into the accumulator).
 // The argmax is not tracked per element: the main loop only records, per output, the first
-// 64-wide chunk of the reduction axis in which the accumulator grew to its final value
+// 32-wide chunk of the reduction axis in which the accumulator grew to its final value
 // (one compare per output per chunk); a second small kernel rescans that one chunk and
 // writes the exact word.  Strict '>' on chunk level followed by "first equal element"
 // inside the chunk is the same total order as the reference's strict '>' element scan.
@@ -29,7 +29,7 @@ struct InfFwdParams {
     int W_CI;       // leading dimension of w
 };
 
-constexpr int CHUNK_TILES = 2;  // argmax chunk = 2 k-tiles = 64 reduction steps
+constexpr int CHUNK_TILES = 1;  // argmax chunk = one k-tile = 32 reduction steps
 
 enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
 
@@ -158,32 +158,55 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams
 }
 
 // Turns the chunk id left in pos by the tracking kernel into the reference's argmax word.
+// One warp owns 32 consecutive outputs of one row; for each of them the 32 lanes load the 32
+// elements of its chunk (coalesced in x, one row segment of W), compare with y and the lowest
+// matching lane gives the index.  Four outputs are in flight per warp to overlap the
+// index -> weight load chains.
 __global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p) {
-    const int n = blockIdx.x * 32 + (threadIdx.x & 31);
+    static_assert(CHUNK_TILES * BK == 32, "one lane per chunk element");
+    const int lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 32;
     const int m = blockIdx.y * 8 + (threadIdx.x >> 5);
-    if (n >= p.CO || m >= p.B) return;
-    const size_t o = (size_t)m * p.CO + n;
-    const int chunk = p.pos[o];
-    if (chunk < 0) {
-        p.pos[o] = 0;
-        return;
-    }
+    if (m >= p.B) return;
     const int s = m / SNB_SUB_BATCH;
-    const float yv = p.y[o];
+    const int n = n0 + lane;
+    const bool have = n < p.CO;
+    const size_t o = (size_t)m * p.CO + n;
+    const int my_chunk = have ? p.pos[o] : -1;
+    const float my_y = have ? p.y[o] : 0.f;
+    const int my_row = have ? (p.co ? p.co[(size_t)s * p.CO + n] : n) : 0;
     const float* xr = p.x + (size_t)m * p.CI;
-    const float* wr = p.w + (size_t)(p.co ? p.co[(size_t)s * p.CO + n] : n) * p.W_CI;
     const int* ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
-    const int c0 = chunk * (CHUNK_TILES * BK);
-    const int c1 = min(p.CI, c0 + CHUNK_TILES * BK);
-    uint32_t word = 0;
-    for (int c = c0; c < c1; c++) {
-        const float t = xr[c] - wr[ci_s ? ci_s[c] : c];
-        if (fabsf(t) == yv) {
-            word = (uint32_t)c | (t >= 0 ? 0u : SNB_SIGN_BIT);
-            break;
+    uint32_t my_word = 0;
+#pragma unroll 1
+    for (int base = 0; base < 32; base += 4) {
+        int col[4];
+        float xv[4], yv[4], wv[4];
+        int rowv[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int chunk = __shfl_sync(0xffffffffu, my_chunk, base + u);
+            yv[u] = __shfl_sync(0xffffffffu, my_y, base + u);
+            rowv[u] = __shfl_sync(0xffffffffu, my_row, base + u);
+            const int c = chunk * 32 + lane;
+            const bool ok = chunk >= 0 && c < p.CI;
+            col[u] = ok ? (ci_s ? ci_s[c] : c) : -1;
+            xv[u] = ok ? xr[c] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) wv[u] = col[u] >= 0 ? p.w[(size_t)rowv[u] * p.W_CI + col[u]] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float t = xv[u] - wv[u];
+            const uint32_t hits = __ballot_sync(0xffffffffu, col[u] >= 0 && fabsf(t) == yv[u]);
+            const int first = hits ? __ffs(hits) - 1 : 0;
+            const float tf = __shfl_sync(0xffffffffu, t, first);
+            const int chunk = __shfl_sync(0xffffffffu, my_chunk, base + u);
+            const uint32_t word = hits ? ((uint32_t)(chunk * 32 + first) | (tf >= 0 ? 0u : SNB_SIGN_BIT)) : 0u;
+            if (lane == base + u) my_word = word;
         }
     }
-    p.pos[o] = (int)word;
+    if (have) p.pos[o] = (int)my_word;
 }
 
 // Sparse backward: one CTA per batch row.  grad_x of the row is accumulated in shared
@@ -239,44 +262,203 @@ __global__ void __launch_bounds__(256) inf_bwd_wide_kernel(const float* __restri
     }
 }
 
-// ---- host side ---------------------------------------------------------------------------
+// Dense forward without argmax words, stream-K over (tile, k-tile) pairs: every CTA of a
+// persistent grid does the same number of k-tiles, partial tiles are merged with atomicMax
+// (exact for max), so the run time does not depend on how the tile count divides the SMs.
+struct InfSkParams {
+    const float* x;
+    const float* w;
+    float* y;
+    int B, CO, CI;
+    int tiles_m, tiles_n;
+};
 
-template <int WM, int WN, int MODE, bool TRACK>
-static cudaError_t launch_fwd(const InfFwdParams& p, cudaStream_t st) {
-    constexpr int BM = 32 * WM, BN = 64 * WN;
+template <int WM, int WN, bool VEC>
+__global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkParams p) {
+    constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;
+    float* ws = smem + 2 * BM * LDS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp / WN, wn = warp % WN, tb = lane >> 3, tj = lane & 7;
+    StreamK sk{p.tiles_m, p.tiles_n, (p.CI + BK - 1) / BK};
+    long long u0, u1;
+    sk.range(u0, u1);
+    while (u0 < u1) {
+        const int tile = (int)(u0 / sk.nk);
+        const int ka = (int)(u0 % sk.nk);
+        const int kb = (int)min((long long)sk.nk, ka + (u1 - u0));
+        const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+        auto stage = [&](int kt, int st) {
+            float* xd = xs + st * BM * LDS;
+            float* wd = ws + st * BN * LDS;
+            if (VEC) {
+                stage_dense_vec<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+                stage_dense_vec<BN, NT>(wd, p.w, n0, p.CO, p.CI, kt * BK, p.CI, tid);
+            } else {
+                stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+                stage_dense_scalar<BN, NT>(wd, p.w, n0, p.CO, p.CI, kt * BK, p.CI, tid);
+            }
+        };
+        float acc[8][8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[i][j] = SNB_EPS;
+        __syncthreads();  // the previous tile's readers are done with both stages
+        stage(ka, ka & 1);
+        cp_async_commit();
+        for (int kt = ka; kt < kb; kt++) {
+            cp_async_wait<0>();
+            __syncthreads();
+            if (kt + 1 < kb) stage(kt + 1, (kt + 1) & 1);
+            cp_async_commit();
+            const float* xr = xs + (kt & 1) * BM * LDS + (wm * 32 + tb) * LDS;
+            const float* wr = ws + (kt & 1) * BN * LDS + (wn * 64 + tj) * LDS;
+#pragma unroll 2
+            for (int kk = 0; kk < BK / 4; kk++) {
+                ulonglong2 xf[8], wf[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    xf[i] = *reinterpret_cast<const ulonglong2*>(xr + i * 4 * LDS + kk * 4);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    wf[j] = *reinterpret_cast<const ulonglong2*>(wr + j * 8 * LDS + kk * 4);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        float a, b;
+                        unpack2(sub2(xf[i].x, wf[j].x), a, b);
+                        acc[i][j] = max3abs(acc[i][j], a, b);
+                        unpack2(sub2(xf[i].y, wf[j].y), a, b);
+                        acc[i][j] = max3abs(acc[i][j], a, b);
+                    }
+                }
+            }
+        }
+        const bool whole = (ka == 0 && kb == sk.nk);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int m = m0 + wm * 32 + tb + 4 * i;
+            if (m >= p.B) continue;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int n = n0 + wn * 64 + tj + 8 * j;
+                if (n >= p.CO) continue;
+                if (whole) p.y[(size_t)m * p.CO + n] = acc[i][j];
+                else atomic_max_nonneg(p.y + (size_t)m * p.CO + n, acc[i][j]);
+            }
+        }
+        u0 += kb - ka;
+    }
+}
+
+template <int WM, int WN, bool VEC>
+static cudaError_t launch_sk(InfSkParams p, cudaStream_t st) {
+    constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
     constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
-    auto kern = inf_fwd_kernel<WM, WN, MODE, TRACK>;
-    static bool configured[64] = {};  // per device
+    auto kern = inf_fwd_sk_kernel<WM, WN, VEC>;
+    static int ctas_per_sm[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    int& cps = ctas_per_sm[dev & 63];
+    if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
-        configured[dev & 63] = true;
+        int occ = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
+        if (e != cudaSuccess) return e;
+        cps = occ > 0 ? occ : 1;
     }
-    dim3 grid((p.B + BM - 1) / BM, (p.CO + BN - 1) / BN);
-    kern<<<grid, WM * WN * 32, SMEM, st>>>(p);
+    p.tiles_m = (p.B + BM - 1) / BM;
+    p.tiles_n = (p.CO + BN - 1) / BN;
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const long long units = tiles * ((p.CI + BK - 1) / BK);
+    long long grid = (long long)sm_count() * cps;
+    if (tiles % grid == 0 || units < grid) grid = tiles;  // whole tiles already balance
+    if (grid != tiles) {
+        cudaError_t e = cudaMemsetAsync(p.y, 0, sizeof(float) * (size_t)p.B * p.CO, st);
+        if (e != cudaSuccess) return e;
+    }
+    kern<<<(unsigned)grid, NT, SMEM, st>>>(p);
     return cudaGetLastError();
 }
 
+static cudaError_t dispatch_sk(const InfFwdParams& q, cudaStream_t st) {
+    InfSkParams p{q.x, q.w, q.y, q.B, q.CO, q.CI, 0, 0};
+    const bool vec = (q.CI % 4 == 0) && aligned16(q.x) && aligned16(q.w);
+    const long big = (long)((q.B + 63) / 64) * ((q.CO + 127) / 128);
+    if (big >= sm_count()) return vec ? launch_sk<2, 2, true>(p, st) : launch_sk<2, 2, false>(p, st);
+    return vec ? launch_sk<1, 2, true>(p, st) : launch_sk<1, 2, false>(p, st);
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+template <int WM, int WN, int MODE, bool TRACK>
+struct FwdLaunch {
+    static constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
+    static constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
+    // Resident CTAs per SM of this instantiation on the current device (cached); 0 on error.
+    static int ctas_per_sm(cudaError_t* err) {
+        static int cached[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        int& cps = cached[dev & 63];
+        if (cps == 0) {
+            auto kern = inf_fwd_kernel<WM, WN, MODE, TRACK>;
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            int occ = 0;
+            if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
+            if (e != cudaSuccess) {
+                *err = e;
+                return 0;
+            }
+            cps = occ > 0 ? occ : 1;
+        }
+        return cps;
+    }
+    // Relative run time: waves x (work per wave per SM).
+    static double cost(const InfFwdParams& p, cudaError_t* err) {
+        const int cps = ctas_per_sm(err);
+        if (cps == 0) return 1e300;
+        const long long tiles = (long long)((p.B + BM - 1) / BM) * ((p.CO + BN - 1) / BN);
+        const long long slots = (long long)sm_count() * cps;
+        const long long waves = (tiles + slots - 1) / slots;
+        return (double)waves * cps * BM * BN;
+    }
+    static cudaError_t launch(const InfFwdParams& p, cudaStream_t st) {
+        cudaError_t err = cudaSuccess;
+        if (ctas_per_sm(&err) == 0) return err;
+        dim3 grid((p.B + BM - 1) / BM, (p.CO + BN - 1) / BN);
+        inf_fwd_kernel<WM, WN, MODE, TRACK><<<grid, NT, SMEM, st>>>(p);
+        return cudaGetLastError();
+    }
+};
+
 template <int MODE, bool TRACK>
 static cudaError_t dispatch_dense(const InfFwdParams& p, cudaStream_t st) {
-    const int sms = sm_count();
-    // Largest tile that still gives every SM a CTA; otherwise the smallest.
-    const long t128 = (long)((p.B + 127) / 128) * ((p.CO + 127) / 128);
-    const long t64 = (long)((p.B + 63) / 64) * ((p.CO + 127) / 128);
-    if (t128 >= sms) return launch_fwd<4, 2, MODE, TRACK>(p, st);
-    if (t64 >= sms) return launch_fwd<2, 2, MODE, TRACK>(p, st);
-    return launch_fwd<1, 2, MODE, TRACK>(p, st);
+    cudaError_t err = cudaSuccess;
+    const double c4 = FwdLaunch<4, 2, MODE, TRACK>::cost(p, &err);
+    const double c2 = FwdLaunch<2, 2, MODE, TRACK>::cost(p, &err);
+    const double c1 = FwdLaunch<1, 2, MODE, TRACK>::cost(p, &err);
+    if (err != cudaSuccess) return err;
+    if (c4 <= c2 && c4 <= c1) return FwdLaunch<4, 2, MODE, TRACK>::launch(p, st);
+    if (c2 <= c1) return FwdLaunch<2, 2, MODE, TRACK>::launch(p, st);
+    return FwdLaunch<1, 2, MODE, TRACK>::launch(p, st);
 }
 
 template <bool TRACK>
 static cudaError_t dispatch_fwd(const InfFwdParams& p, cudaStream_t st) {
     if (p.ci || p.co) {
-        const long t256 = (long)((p.B + 31) / 32) * ((p.CO + 255) / 256);
-        if (t256 >= sm_count()) return launch_fwd<1, 4, MODE_GATHER, TRACK>(p, st);
-        return launch_fwd<1, 2, MODE_GATHER, TRACK>(p, st);
+        cudaError_t err = cudaSuccess;
+        const double c4 = FwdLaunch<1, 4, MODE_GATHER, TRACK>::cost(p, &err);
+        const double c2 = FwdLaunch<1, 2, MODE_GATHER, TRACK>::cost(p, &err);
+        if (err != cudaSuccess) return err;
+        return c4 <= c2 ? FwdLaunch<1, 4, MODE_GATHER, TRACK>::launch(p, st)
+                        : FwdLaunch<1, 2, MODE_GATHER, TRACK>::launch(p, st);
     }
+    if (!TRACK) return dispatch_sk(p, st);
     const bool vec = (p.CI % 4 == 0) && (p.W_CI % 4 == 0) && aligned16(p.x) && aligned16(p.w);
     return vec ? dispatch_dense<MODE_VEC, TRACK>(p, st) : dispatch_dense<MODE_SCALAR, TRACK>(p, st);
 }

@@ -50,16 +50,24 @@ __device__ __forceinline__ void stage_dense_scalar(float* s, const float* __rest
 // adjacent); every thread keeps the element offsets of its ROWS / (NT / 8) rows in registers.
 template <int ROWS, int NT>
 struct GatherW {
+    static_assert(NT == 64 || NT == 128 || NT == 256, "group_row assumes 2, 4 or 8 warps");
     static constexpr int RPT = ROWS / (NT / 8);
     int rowoff[RPT];  // element offset of the row start in W, or -1 past the last row
     int col[4];       // W column of this thread's four k positions in the next k-tile, or -1
 
+    // Row of the tile handled by 8-lane group `grp` in pass 0.  The four groups of a warp take
+    // rows two apart (bank offset 8 words with the 36-float stride), so the 32 four-byte
+    // shared-memory writes of one warp instruction hit 32 distinct banks.
+    __device__ __forceinline__ static int group_row(int tid) {
+        const int w = tid >> 5, g = (tid >> 3) & 3;
+        return 2 * g + (w & 1) + 8 * (w >> 1);
+    }
     __device__ __forceinline__ void init_rows(const int* __restrict__ co_s, int n0, int CO,
                                               int W_CI, int tid) {
-        const int grp = tid >> 3;
+        const int r0 = group_row(tid);
 #pragma unroll
         for (int i = 0; i < RPT; i++) {
-            int n = n0 + grp + (NT / 8) * i;
+            int n = n0 + r0 + (NT / 8) * i;
             rowoff[i] = n < CO ? (co_s ? co_s[n] : n) * W_CI : -1;
         }
     }
@@ -72,14 +80,14 @@ struct GatherW {
         }
     }
     __device__ __forceinline__ void stage(float* s, const float* __restrict__ w, int tid) const {
-        const int grp = tid >> 3, l8 = tid & 7;
+        const int r0 = group_row(tid), l8 = tid & 7;
 #pragma unroll
         for (int i = 0; i < RPT; i++) {
 #pragma unroll
             for (int m = 0; m < 4; m++) {
                 bool ok = (rowoff[i] >= 0) && (col[m] >= 0);
                 const float* src = ok ? w + rowoff[i] + col[m] : w;
-                cp_async4(smem_u32(s + (grp + (NT / 8) * i) * LDS + l8 + 8 * m), src, ok ? 4 : 0);
+                cp_async4(smem_u32(s + (r0 + (NT / 8) * i) * LDS + l8 + 8 * m), src, ok ? 4 : 0);
             }
         }
     }

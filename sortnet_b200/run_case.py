@@ -4,7 +4,7 @@
 
 Used for quick timing of a single kernel and as the small, self-terminating command that
 profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_nograd,
-inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, mean_shift.
+inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, mean_shift, probe (hardware probes).
 """
 import argparse
 
@@ -14,6 +14,56 @@ from . import norm_dist_cuda as C
 from .layers import sample_mask
 
 OPS_PER_ELEMENT = {"inf_fwd": 2, "inf_nograd": 2, "bound_nograd": 6, "bound_fwd": 6, "lp_fwd": 4, "lp_bwd": 6}
+
+
+PROBES = ["packed sub + max3abs", "2 scalar sub + 2 max", "2 scalar sub + max3abs", "packed sub + 2 max",
+          "max3abs alone", "interval-bound step (2 sub, min3, max3 per element)", "p=8 step (sub2, mul2, mul2, fma2)"]
+
+
+def probe():
+    """Times the FP32 FMA probe and every instruction form of the inner step; prints element
+    rates per clock per SM using the SM clock NVML reports while the probes run."""
+    import ctypes
+    from . import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    scratch = torch.linspace(0, 1, 2 * sms * 256 + 64, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    mhz = None
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(0)
+    except Exception:
+        h = None
+
+    def timed(launch):
+        best = float("inf")
+        for _ in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return best
+
+    flops = ctypes.c_double()
+    for _ in range(3):   # let the clocks ramp
+        lib.snb_probe_fp32(scratch.data_ptr(), 1 << 16, ctypes.byref(flops), st)
+    torch.cuda.synchronize()
+    ms = timed(lambda: lib.snb_probe_fp32(scratch.data_ptr(), 1 << 14, ctypes.byref(flops), st))
+    if h is not None:
+        mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+    print("FP32 FMA probe: %.1f GFLOP/s (2 flops per FMA), SM clock %s MHz, %d SMs" % (flops.value / ms * 1e-6, mhz, sms))
+    clk = (mhz or 1965) * 1e6
+    pairs = ctypes.c_double()
+    for v, name in enumerate(PROBES):
+        ms = timed(lambda: lib.snb_probe_step(v, scratch.data_ptr(), 4000, ctypes.byref(pairs), st))
+        elems = 2 * pairs.value
+        print("variant %d %-52s %7.3f ms  %6.2f elements/clock/SM  %5.2f issue-cycles per element per scheduler"
+              % (v, name, ms, elems / (ms * 1e-3) / clk / sms, 128.0 / (elems / (ms * 1e-3) / clk / sms)))
 
 
 def main():
@@ -27,6 +77,8 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     a = ap.parse_args()
+    if a.op == "probe":
+        return probe()
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
     S = (a.B + 31) // 32
