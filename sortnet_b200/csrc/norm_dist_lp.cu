@@ -12,8 +12,9 @@
 // The reference reaches the p > 10 value with an online running maximum that may lag the true
 // maximum by 1e-6 relative; here M is the exact maximum, computed first by the l-infinity
 // kernel into y, so the result is the exact-math value up to fp32 rounding.  Integer p in
-// [1, 8] uses multiply chains (as the reference does), any other p uses exp2(p * log2 r) with
-// the full-precision log2f / exp2f so that the p-fold error amplification stays inside 1e-5.
+// [1, 8] uses multiply chains (as the reference does), any other p uses ex2(p * log2 r) on the
+// special-function unit with a series for log2 near r = 1 (log2_rel), which keeps the p-fold
+// amplification of the logarithm's error at the level of the fp32 rounding of r itself.
 #include <float.h>
 #include "tile.cuh"
 #include "launch.h"
@@ -24,7 +25,46 @@ namespace snb {
 cudaError_t inf_forward_values(const float* x, const float* w, float* y, const int* ci, const int* co,
                                int B, int CO, int CI, int W_CI, cudaStream_t st);
 
-// |r|^IP for integer IP (multiply chain) or r^e for IP < 0 (r >= 0).
+// Special-function-unit exp2 / log2.  The .ftz forms skip the denormal fix-up code: a denormal
+// argument of log2 reads as 0 (its power is 0 to fp32 anyway) and results below 2^-126 flush to 0.
+__device__ __forceinline__ float ex2_approx(float z) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(z));
+    return r;
+}
+__device__ __forceinline__ float lg2_approx(float a) {
+    float r;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+    return r;
+}
+
+// log2(a) by a degree-8 series in d = a - 1 (exact subtraction), for |d| <= 0.125.  The hardware
+// approximation has an absolute error of 2^-22, i.e. no relative accuracy near a = 1; the series
+// keeps the relative error of log2 at fp32 level there, so that a^e for large e is as accurate as
+// the fp32 rounding of a allows.
+__device__ __forceinline__ float log2_series(float a) {
+    const float d = a - 1.0f;
+    float s = fmaf(d, -0.125f, 1.0f / 7.0f);
+    s = fmaf(d, s, -1.0f / 6.0f);
+    s = fmaf(d, s, 0.2f);
+    s = fmaf(d, s, -0.25f);
+    s = fmaf(d, s, 1.0f / 3.0f);
+    s = fmaf(d, s, -0.5f);
+    s = fmaf(d, s, 1.0f);
+    return d * 1.4426950408889634f * s;
+}
+__device__ __forceinline__ bool near_one(float a) { return fabsf(a - 1.0f) <= 0.125f; }
+
+// a^e for a >= 0, accurate per value (used once per output and in the backward).
+__device__ __forceinline__ float pow_pos(float a, float e) {
+    return ex2_approx(e * (near_one(a) ? log2_series(a) : lg2_approx(a)));
+}
+// a^e where only the *sum* of many such terms matters (forward): the absolute error of the
+// hardware log2 perturbs the sum by ~1.7e-7 * e relative, and the e-th root taken afterwards
+// divides that by e.
+__device__ __forceinline__ float pow_pos_sum(float a, float e) { return ex2_approx(e * lg2_approx(a)); }
+
+// |r|^IP for integer IP (multiply chain) or |r|^e for IP < 0; forward terms.
 template <int IP>
 __device__ __forceinline__ float pow_abs(float r, float e) {
     if (IP == 0) return 1.0f;
@@ -36,10 +76,10 @@ __device__ __forceinline__ float pow_abs(float r, float e) {
     if (IP == 6) { float a = r * r; return a * a * a; }
     if (IP == 7) { float a = r * r; return fabsf(r) * a * a * a; }
     if (IP == 8) { float a = r * r; a = a * a; return a * a; }
-    return exp2f(e * log2f(fabsf(r)));
+    return pow_pos_sum(fabsf(r), e);
 }
 
-// sgn(r) * |r|^IP.
+// sgn(r) * |r|^IP; backward terms.
 template <int IP>
 __device__ __forceinline__ float pow_signed(float r, float e) {
     if (IP == 0) return r >= 0 ? 1.0f : -1.0f;
@@ -50,7 +90,7 @@ __device__ __forceinline__ float pow_signed(float r, float e) {
     if (IP == 5) { float a = r * r; return a * a * r; }
     if (IP == 6) { float a = r * r; return fabsf(r) * r * a * a; }
     if (IP == 7) { float a = r * r; return a * a * a * r; }
-    return copysignf(exp2f(e * log2f(fabsf(r))), r);
+    return copysignf(pow_pos(fabsf(r), e), r);
 }
 
 struct LpFwdParams {
@@ -113,6 +153,9 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
             }
         }
 
+    // worth testing only when most elements qualify: at p >= 48 the cut is |t|/M < 0.56
+    const bool use_skip = NORMALISED && p.p >= 48.0f;
+    const float skip_below = exp2f(-40.0f / p.p);
     stage(0, 0);
     cp_async_commit();
     for (int kt = 0; kt < nk; kt++) {
@@ -135,15 +178,29 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
             for (int j = 0; j < 8; j++) wf[j] = *reinterpret_cast<const float2*>(wr + j * 8 * LDS + kk * 2);
 #pragma unroll
             for (int i = 0; i < 8; i++) {
+                if (NORMALISED) {
+                    // 16 normalised magnitudes at a time: one warp vote decides whether any of them
+                    // can matter, and the special-function chains of the 16 stay independent
+                    float a0[8], a1[8], big = 0.f;
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    float t0 = xf[i].x - wf[j].x, t1 = xf[i].y - wf[j].y;
-                    if (NORMALISED) {
-                        t0 *= rm[i][j];
-                        t1 *= rm[i][j];
+                    for (int j = 0; j < 8; j++) {
+                        a0[j] = fabsf(xf[i].x - wf[j].x) * rm[i][j];
+                        a1[j] = fabsf(xf[i].y - wf[j].y) * rm[i][j];
+                        big = fmaxf(big, fmaxf(a0[j], a1[j]));
                     }
-                    acc[i][j] += pow_abs<IP>(t0, p.p);
-                    acc[i][j] += pow_abs<IP>(t1, p.p);
+                    // (|t|/M)^p < 2^-40 for every element and lane: nothing to add (the sum is >= 1)
+                    if (use_skip && __all_sync(0xffffffffu, big < skip_below)) continue;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        acc[i][j] += pow_abs<IP>(a0[j], p.p);
+                        acc[i][j] += pow_abs<IP>(a1[j], p.p);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        acc[i][j] += pow_abs<IP>(xf[i].x - wf[j].x, p.p);
+                        acc[i][j] += pow_abs<IP>(xf[i].y - wf[j].y, p.p);
+                    }
                 }
             }
         }
@@ -158,8 +215,8 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
             const int n = n0 + wn * 64 + tj + 8 * j;
             if (n >= p.CO) continue;
             float r;
-            if (NORMALISED) r = exp2f(rp * log2f(acc[i][j])) / rm[i][j];
-            else r = exp2f(rp * log2f(fmaxf(acc[i][j], FLT_MIN)));
+            if (NORMALISED) r = pow_pos(acc[i][j], rp) / rm[i][j];
+            else r = pow_pos(fmaxf(acc[i][j], FLT_MIN), rp);
             p.y[(size_t)m * p.CO + n] = r;
         }
     }
@@ -178,18 +235,24 @@ struct LpBwdParams {
     float pm1;  // p - 1
 };
 
-// One CTA = one 32-row sub-batch x 256 compact input columns; it walks all outputs j.
-// Thread (tb, tc): rows tb*8 .. tb*8+7, columns 4*tc .. 4*tc+3; the four tb lanes that share
-// tc sit in one warp (lane = (tc % 8) * 4 + tb), so the per-(j, c) sums over the 32 rows
-// finish with two shuffles and one global reduction.
-template <int IP>
-__global__ void __launch_bounds__(256) lp_bwd_kernel(const LpBwdParams p) {
-    constexpr int JT = 32;
-    __shared__ float2 gr[JT][32 + 1];  // (g, 1/y) for [j][b]
+// One CTA (NT threads) = one 32-row sub-batch x NT compact input columns; it walks all outputs j in tiles
+// of 32.  Thread (tb, tc): rows tb*8 .. tb*8+7, columns 4*tc .. 4*tc+3; the four tb lanes that
+// share tc sit in one warp (lane = (tc % 8) * 4 + tb), so the per-(j, c) sums over the 32 rows
+// finish with two shuffles and one global reduction.  The gathered W tile [32 j][NT c] and the
+// (g, y) tile of the next j-tile are fetched with cp.async while the current one is consumed.
+constexpr int LPB_JT = 32;
+
+template <int IP, int NT>
+__global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
+    constexpr int LPB_WLD = NT + 4;  // floats per W-tile row (+4: keeps 16-byte alignment, shifts banks)
+    extern __shared__ __align__(16) float smem[];
+    float* wt = smem;                                   // [2][JT][WLD]
+    float* gt = smem + 2 * LPB_JT * LPB_WLD;            // [2][JT][33]  g
+    float* yt = gt + 2 * LPB_JT * 33;                   // [2][JT][33]  y, turned into 1/y in place
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tb = lane & 3, tc = warp * 8 + (lane >> 2);
     const int s = blockIdx.x, b0 = s * SNB_SUB_BATCH;
-    const int c0 = blockIdx.y * 256 + tc * 4;
+    const int c0 = blockIdx.y * NT + tc * 4;
     const int* ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
     const int* co_s = p.co ? p.co + (size_t)s * p.CO : nullptr;
 
@@ -206,38 +269,113 @@ __global__ void __launch_bounds__(256) lp_bwd_kernel(const LpBwdParams p) {
             gx[i][k] = 0.f;
         }
 
-    for (int j0 = 0; j0 < p.CO; j0 += JT) {
-        __syncthreads();
-        for (int e = tid; e < JT * 32; e += 256) {
-            const int jj = e & 31, bb = e >> 5;  // consecutive threads -> consecutive j (coalesced)
-            const int b = b0 + bb, j = j0 + jj;
-            float2 v = make_float2(0.f, 0.f);
-            if (b < p.B && j < p.CO) {
-                v.x = p.g[(size_t)b * p.CO + j];
-                v.y = 1.0f / p.y[(size_t)b * p.CO + j];
-            }
-            gr[jj][bb] = v;
-        }
-        __syncthreads();
-        const int jn = min(JT, p.CO - j0);
-        for (int jj = 0; jj < jn; jj++) {
-            const int row = co_s ? co_s[j0 + jj] : j0 + jj;
+    const int ntiles = (p.CO + LPB_JT - 1) / LPB_JT;
+    // |u|^(p-1) < 2^-40 for a whole warp: the terms are dropped (the largest terms are ~1)
+    const bool use_skip = p.pm1 >= 48.0f;
+    const float skip_below = IP < 0 ? exp2f(-40.0f / fmaxf(p.pm1, 1e-3f)) : 0.f;
+    // this thread stages rows jj = tb, tb + 4, ... of the W tile (its own four columns) and
+    // elements e = tid, tid + NT, ... of the 32 x 32 (g, y) tiles
+    auto stage = [&](int t, int st) {
+        const int j0 = t * LPB_JT;
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            const int jj = tb + 4 * r, j = j0 + jj;
+            const bool jok = j < p.CO;
+            const int row = jok ? (co_s ? co_s[j] : j) : 0;
             const float* wrow = p.w + (size_t)row * p.W_CI;
-            float wv[4], gwp[4];
 #pragma unroll
             for (int k = 0; k < 4; k++) {
-                wv[k] = col[k] >= 0 ? wrow[col[k]] : 0.f;
-                gwp[k] = 0.f;
+                const bool ok = jok && col[k] >= 0;
+                cp_async4(smem_u32(wt + (st * LPB_JT + jj) * LPB_WLD + tc * 4 + k), ok ? wrow + col[k] : p.w, ok ? 4 : 0);
             }
+        }
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float2 gy = gr[jj][tb * 8 + i];
+        for (int r = 0; r < 1024 / NT; r++) {
+            const int e = tid + NT * r;
+            const int jj = e & 31, bb = e >> 5;  // consecutive threads -> consecutive j (coalesced)
+            const int b = b0 + bb, j = j0 + jj;
+            const bool ok = b < p.B && j < p.CO;
+            const size_t o = ok ? (size_t)b * p.CO + j : 0;
+            cp_async4(smem_u32(gt + (st * LPB_JT + jj) * 33 + bb), p.g + o, ok ? 4 : 0);
+            cp_async4(smem_u32(yt + (st * LPB_JT + jj) * 33 + bb), p.y + o, ok ? 4 : 0);
+        }
+    };
+
+    stage(0, 0);
+    cp_async_commit();
+    for (int t = 0; t < ntiles; t++) {
+        const int st = t & 1;
+        cp_async_wait<0>();
+        __syncthreads();                       // tile t landed; everyone is done with tile t - 1
+        if (t + 1 < ntiles) stage(t + 1, st ^ 1);
+        cp_async_commit();
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const float u = (xv[i][k] - wv[k]) * gy.y;
-                    const float term = gy.x * pow_signed<IP>(u, p.pm1);
-                    gx[i][k] += term;
-                    gwp[k] += term;
+        for (int r = 0; r < 1024 / NT; r++) {  // y -> 1/y (0 for padding), each thread its own elements
+            const int e = tid + NT * r;
+            float* q = yt + (st * LPB_JT + (e & 31)) * 33 + (e >> 5);
+            const float v = *q;
+            *q = v > 0.f ? 1.0f / v : 0.f;
+        }
+        __syncthreads();
+        const int j0 = t * LPB_JT;
+        const int jn = min(LPB_JT, p.CO - j0);
+        for (int jj = 0; jj < jn; jj++) {
+            const float4 wv4 = *reinterpret_cast<const float4*>(wt + (st * LPB_JT + jj) * LPB_WLD + tc * 4);
+            const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+            float gwp[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* gp = gt + (st * LPB_JT + jj) * 33 + tb * 8;
+            const float* yp = yt + (st * LPB_JT + jj) * 33 + tb * 8;
+            if (IP >= 0) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float gv = gp[i], ry = yp[i];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float u = (xv[i][k] - wv[k]) * ry;
+                        const float term = gv * pow_signed<IP>(u, p.pm1);
+                        gx[i][k] += term;
+                        gwp[k] += term;
+                    }
+                }
+            } else {
+                // general exponent: 16 terms at a time so that their log2 / exp2 chains overlap;
+                // one vote per batch for "all negligible" and one for "some ratio is near 1"
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    float u[4][4], lg[4][4], big = 0.f;
+                    bool near = false;
+#pragma unroll
+                    for (int ii = 0; ii < 4; ii++) {
+                        const float ry = yp[4 * h + ii];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            u[ii][k] = (xv[4 * h + ii][k] - wv[k]) * ry;
+                            const float a = fabsf(u[ii][k]);
+                            big = fmaxf(big, a);
+                            near = near || near_one(a);
+                            lg[ii][k] = lg2_approx(a);
+                        }
+                    }
+                    if (use_skip && __all_sync(0xffffffffu, big < skip_below)) continue;
+                    if (__any_sync(0xffffffffu, near)) {
+#pragma unroll
+                        for (int ii = 0; ii < 4; ii++)
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const float a = fabsf(u[ii][k]);
+                                if (near_one(a)) lg[ii][k] = log2_series(a);
+                            }
+                    }
+#pragma unroll
+                    for (int ii = 0; ii < 4; ii++) {
+                        const float gv = gp[4 * h + ii];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const float term = gv * copysignf(ex2_approx(p.pm1 * lg[ii][k]), u[ii][k]);
+                            gx[4 * h + ii][k] += term;
+                            gwp[k] += term;
+                        }
+                    }
                 }
             }
             if (p.gw) {
@@ -247,6 +385,7 @@ __global__ void __launch_bounds__(256) lp_bwd_kernel(const LpBwdParams p) {
                     gwp[k] += __shfl_xor_sync(0xffffffffu, gwp[k], 2);
                 }
                 if (tb == 0) {
+                    const int row = co_s ? co_s[j0 + jj] : j0 + jj;
 #pragma unroll
                     for (int k = 0; k < 4; k++)
                         if (col[k] >= 0) atomicAdd(p.gw + (size_t)row * p.W_CI + col[k], -gwp[k]);
@@ -262,6 +401,53 @@ __global__ void __launch_bounds__(256) lp_bwd_kernel(const LpBwdParams p) {
         for (int k = 0; k < 4; k++)
             if (col[k] >= 0) p.gx[(size_t)b * p.CI + c0 + k] = gx[i][k];
     }
+}
+
+template <int IP, int NT>
+struct LpBwdLaunch {
+    static constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * 33) * (int)sizeof(float);
+    static int ctas_per_sm(cudaError_t* err) {
+        static int cached[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        int& cps = cached[dev & 63];
+        if (cps == 0) {
+            auto kern = lp_bwd_kernel<IP, NT>;
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            int occ = 0;
+            if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
+            if (e != cudaSuccess) {
+                *err = e;
+                return 0;
+            }
+            cps = occ > 0 ? occ : 1;
+        }
+        return cps;
+    }
+    static double cost(const LpBwdParams& q, cudaError_t* err) {
+        const int cps = ctas_per_sm(err);
+        if (cps == 0) return 1e300;
+        const long long ctas = (long long)((q.B + 31) / 32) * ((q.CI + NT - 1) / NT);
+        const long long slots = (long long)sm_count() * cps;
+        return (double)((ctas + slots - 1) / slots) * cps * NT;
+    }
+    static cudaError_t launch(const LpBwdParams& q, cudaStream_t st) {
+        cudaError_t err = cudaSuccess;
+        if (ctas_per_sm(&err) == 0) return err;
+        dim3 grid((q.B + 31) / 32, (q.CI + NT - 1) / NT);
+        lp_bwd_kernel<IP, NT><<<grid, NT, SMEM, st>>>(q);
+        return cudaGetLastError();
+    }
+};
+
+// Column-tile width (= threads per CTA) with the fewest waves x work per wave.
+template <int IP>
+static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
+    cudaError_t err = cudaSuccess;
+    const double c256 = LpBwdLaunch<IP, 256>::cost(q, &err);
+    const double c128 = LpBwdLaunch<IP, 128>::cost(q, &err);
+    if (err != cudaSuccess) return err;
+    return c256 <= c128 ? LpBwdLaunch<IP, 256>::launch(q, st) : LpBwdLaunch<IP, 128>::launch(q, st);
 }
 
 template <int WN, int MODE, int IP, bool NORM>
@@ -340,17 +526,16 @@ static int lp_backward(const float* g, const float* x, const float* w, const flo
         return SNB_ERR_TOO_LARGE;
     if (gw) SNB_CUDA(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)W_CO * W_CI, st));
     LpBwdParams q{g, x, w, y, gx, gw, ci, co, B, CO, CI, W_CI, p - 1.0f};
-    dim3 grid((B + 31) / 32, (CI + 255) / 256);
     switch (integer_power(p - 1.0f)) {
-        case 0: lp_bwd_kernel<0><<<grid, 256, 0, st>>>(q); break;
-        case 1: lp_bwd_kernel<1><<<grid, 256, 0, st>>>(q); break;
-        case 2: lp_bwd_kernel<2><<<grid, 256, 0, st>>>(q); break;
-        case 3: lp_bwd_kernel<3><<<grid, 256, 0, st>>>(q); break;
-        case 4: lp_bwd_kernel<4><<<grid, 256, 0, st>>>(q); break;
-        case 5: lp_bwd_kernel<5><<<grid, 256, 0, st>>>(q); break;
-        case 6: lp_bwd_kernel<6><<<grid, 256, 0, st>>>(q); break;
-        case 7: lp_bwd_kernel<7><<<grid, 256, 0, st>>>(q); break;
-        default: lp_bwd_kernel<-1><<<grid, 256, 0, st>>>(q); break;
+        case 0: SNB_CUDA(launch_lp_bwd<0>(q, st)); break;
+        case 1: SNB_CUDA(launch_lp_bwd<1>(q, st)); break;
+        case 2: SNB_CUDA(launch_lp_bwd<2>(q, st)); break;
+        case 3: SNB_CUDA(launch_lp_bwd<3>(q, st)); break;
+        case 4: SNB_CUDA(launch_lp_bwd<4>(q, st)); break;
+        case 5: SNB_CUDA(launch_lp_bwd<5>(q, st)); break;
+        case 6: SNB_CUDA(launch_lp_bwd<6>(q, st)); break;
+        case 7: SNB_CUDA(launch_lp_bwd<7>(q, st)); break;
+        default: SNB_CUDA(launch_lp_bwd<-1>(q, st)); break;
     }
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;

@@ -4,7 +4,7 @@
 
 Used for quick timing of a single kernel and as the small, self-terminating command that
 profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_nograd,
-inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, mean_shift, probe (hardware probes).
+inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_shift, probe (hardware probes).
 """
 import argparse
 
@@ -13,7 +13,7 @@ import torch
 from . import norm_dist_cuda as C
 from .layers import sample_mask
 
-OPS_PER_ELEMENT = {"inf_fwd": 2, "inf_nograd": 2, "bound_nograd": 6, "bound_fwd": 6, "lp_fwd": 4, "lp_bwd": 6}
+OPS_PER_ELEMENT = {"inf_fwd": 2, "inf_nograd": 2, "bound_nograd": 6, "bound_fwd": 6, "lp_fwd": 4, "lp_bwd": 6, "lp_bwd_x": 6}
 
 
 PROBES = ["packed sub + max3abs", "2 scalar sub + 2 max", "2 scalar sub + max3abs", "packed sub + 2 max",
@@ -100,7 +100,7 @@ def main():
 
     if a.op in ("inf_bwd",):
         C.inf_dist_forward(x, w, y, pos, 1, ci, co)
-    if a.op == "lp_bwd":
+    if a.op in ("lp_bwd", "lp_bwd_x"):
         C.norm_dist_forward(x, w, y, 1, a.p, ci, co)
 
     def run():
@@ -118,6 +118,8 @@ def main():
             C.norm_dist_forward(x, w, y, 1, a.p, ci, co)
         elif a.op == "lp_bwd":
             C.norm_dist_backward_input_weight(g, x, w, y, gx, gw, 1, a.p, ci, co)
+        elif a.op == "lp_bwd_x":
+            C.norm_dist_backward_input(g, x, w, y, gx, 1, a.p, ci, co)
         elif a.op == "mean_shift":
             C.mean_shift_stats(y.copy_(g), co, mean, None, 0.1)
             C.mean_shift_apply(y, mean, co, y)
