@@ -28,6 +28,8 @@
 #ifndef SORTNET_B200_H
 #define SORTNET_B200_H
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -62,6 +64,19 @@ int snb_probe_step(int variant, float* scratch, int iters, double* pairs, void* 
 int snb_inf_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
                          float* y, int* pos, const int* w_index_ci, const int* w_index_co,
                          int W_CO, int W_CI, void* stream);
+
+/* The same operation with caller-provided scratch memory.  Without masks the kernel can then
+ * share output tiles between thread blocks along the reduction axis (every SM gets the same
+ * amount of work whatever the shape) and merge the partial (value, position) pairs with 64-bit
+ * atomics in `workspace`; with masks, or when workspace is NULL / smaller than
+ * snb_inf_dist_forward_workspace_bytes(B, CO) = 8 * B * CO bytes, it behaves exactly like
+ * snb_inf_dist_forward.  The workspace needs 8-byte alignment, may hold anything on entry and holds
+ * nothing of value on return; results are bit-identical to snb_inf_dist_forward.
+ * No counterpart in the reference (its launcher has no scratch argument). */
+size_t snb_inf_dist_forward_workspace_bytes(int B, int CO);
+int snb_inf_dist_forward_ws(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                            float* y, int* pos, const int* w_index_ci, const int* w_index_co,
+                            int W_CO, int W_CI, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Same y without pos, unmasked.  Replaces inf_dist::forward_nograd (norm_dist.h:22-23;
  * inf_dist_cuda.cu:277-304). */

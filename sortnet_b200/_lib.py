@@ -3,7 +3,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libsortnet_b200.so")
+# SORTNET_B200_LIB lets a caller point at a library built elsewhere (e.g. an experimental build).
+LIB_PATH = os.environ.get("SORTNET_B200_LIB") or os.path.join(HERE, "libsortnet_b200.so")
 
 _lib = None
 
@@ -14,6 +15,7 @@ _F = ctypes.c_float
 # name -> argument types (every function returns int status)
 SIGNATURES = {
     "snb_inf_dist_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
+    "snb_inf_dist_forward_ws": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, ctypes.c_size_t, _P],
     "snb_inf_dist_forward_nograd": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
     "snb_inf_dist_backward_input": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
     "snb_inf_dist_backward_input_weight": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
@@ -59,6 +61,8 @@ def load(build_if_missing: bool = False):
     lib.snb_last_cuda_error.restype = ctypes.c_char_p
     lib.snb_version.argtypes = []
     lib.snb_version.restype = ctypes.c_int
+    lib.snb_inf_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int]
+    lib.snb_inf_dist_forward_workspace_bytes.restype = ctypes.c_size_t
     _lib = lib
     return lib
 

@@ -16,6 +16,10 @@
 #include "tile.cuh"
 #include "launch.h"
 
+#ifndef SNB_LINF_FORM
+#define SNB_LINF_FORM 0
+#endif
+
 namespace snb {
 
 struct InfFwdParams {
@@ -31,7 +35,38 @@ struct InfFwdParams {
 
 constexpr int CHUNK_TILES = 1;  // argmax chunk = one k-tile = 32 reduction steps
 
-enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
+enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };  // inf_fwd_kernel is only instantiated for GATHER
+
+// Four reduction steps of one output: acc = max(acc, |x_k - w_k|), k = 0..3, operands given as
+// two 64-bit register pairs each.  All instruction forms of subtract + max cost two issue cycles
+// per element on sm_100a; the form is chosen for the fewest auxiliary instructions.
+__device__ __forceinline__ void linf_step(float& acc, const ulonglong2& x, const ulonglong2& w) {
+#if SNB_LINF_FORM == 1      // scalar subtracts + three-input max
+    float x0, x1, x2, x3, w0, w1, w2, w3;
+    unpack2(x.x, x0, x1);
+    unpack2(x.y, x2, x3);
+    unpack2(w.x, w0, w1);
+    unpack2(w.y, w2, w3);
+    acc = max3abs(acc, x0 - w0, x1 - w1);
+    acc = max3abs(acc, x2 - w2, x3 - w3);
+#elif SNB_LINF_FORM == 2    // scalar subtracts + two-input max
+    float x0, x1, x2, x3, w0, w1, w2, w3;
+    unpack2(x.x, x0, x1);
+    unpack2(x.y, x2, x3);
+    unpack2(w.x, w0, w1);
+    unpack2(w.y, w2, w3);
+    acc = fmaxf(acc, fabsf(x0 - w0));
+    acc = fmaxf(acc, fabsf(x1 - w1));
+    acc = fmaxf(acc, fabsf(x2 - w2));
+    acc = fmaxf(acc, fabsf(x3 - w3));
+#else                       // packed subtracts + three-input max
+    float a, b;
+    unpack2(sub2(x.x, w.x), a, b);
+    acc = max3abs(acc, a, b);
+    unpack2(sub2(x.y, w.y), a, b);
+    acc = max3abs(acc, a, b);
+#endif
+}
 
 template <int WM, int WN, int MODE, bool TRACK>
 __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams p) {
@@ -116,11 +151,7 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams
             for (int i = 0; i < 8; i++) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    float a, b;
-                    unpack2(sub2(xf[i].x, wf[j].x), a, b);
-                    acc[i][j] = max3abs(acc[i][j], a, b);
-                    unpack2(sub2(xf[i].y, wf[j].y), a, b);
-                    acc[i][j] = max3abs(acc[i][j], a, b);
+                    linf_step(acc[i][j], xf[i], wf[j]);
                 }
             }
         }
@@ -162,7 +193,10 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams
 // elements of its chunk (coalesced in x, one row segment of W), compare with y and the lowest
 // matching lane gives the index.  Four outputs are in flight per warp to overlap the
 // index -> weight load chains.
-__global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p) {
+// FROM_WS: the tracking kernel ran split over k and left (value bits << 32 | ~chunk) keys in the
+// 64-bit workspace instead of y / pos; y is written here too.
+template <bool FROM_WS>
+__global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, const unsigned long long* __restrict__ keys) {
     static_assert(CHUNK_TILES * BK == 32, "one lane per chunk element");
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * 32;
@@ -172,8 +206,19 @@ __global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p) 
     const int n = n0 + lane;
     const bool have = n < p.CO;
     const size_t o = (size_t)m * p.CO + n;
-    const int my_chunk = have ? p.pos[o] : -1;
-    const float my_y = have ? p.y[o] : 0.f;
+    int my_chunk = -1;
+    float my_y = 0.f;
+    if (have) {
+        if (FROM_WS) {
+            const unsigned long long key = keys[o];
+            my_y = __uint_as_float((uint32_t)(key >> 32));
+            my_chunk = (int)(0xffffffffu - (uint32_t)key);      // 0xffffffff - 0 = -1: no chunk
+            p.y[o] = my_y;
+        } else {
+            my_chunk = p.pos[o];
+            my_y = p.y[o];
+        }
+    }
     const int my_row = have ? (p.co ? p.co[(size_t)s * p.CO + n] : n) : 0;
     const float* xr = p.x + (size_t)m * p.CI;
     const int* ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
@@ -269,11 +314,18 @@ struct InfSkParams {
     const float* x;
     const float* w;
     float* y;
+    int* pos;                   // TRACK without workspace: receives chunk ids
+    unsigned long long* keys;   // TRACK split over k: (value bits << 32 | 0xffffffff - chunk), zeroed
     int B, CO, CI;
     int tiles_m, tiles_n;
 };
 
-template <int WM, int WN, bool VEC>
+__device__ __forceinline__ unsigned long long pack_key(float v, uint32_t chunk16) {
+    const uint32_t lo = chunk16 == 0xffffu ? 0u : 0xffffffffu - chunk16;
+    return ((unsigned long long)__float_as_uint(v) << 32) | lo;
+}
+
+template <int WM, int WN, bool VEC, bool TRACK>
 __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkParams p) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
     extern __shared__ __align__(16) float smem[];
@@ -301,10 +353,21 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
             }
         };
         float acc[8][8];
+        float prev[TRACK ? 8 : 1][TRACK ? 8 : 1];
+        uint32_t q[TRACK ? 8 : 1][TRACK ? 4 : 1];  // two 16-bit chunk ids per word, 0xffff = none
 #pragma unroll
         for (int i = 0; i < 8; i++)
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[i][j] = SNB_EPS;
+        if (TRACK) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) prev[i][j] = SNB_EPS;
+#pragma unroll
+                for (int j = 0; j < 4; j++) q[i][j] = 0xffffffffu;
+            }
+        }
         __syncthreads();  // the previous tile's readers are done with both stages
         stage(ka, ka & 1);
         cp_async_commit();
@@ -328,11 +391,19 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
                 for (int i = 0; i < 8; i++) {
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
-                        float a, b;
-                        unpack2(sub2(xf[i].x, wf[j].x), a, b);
-                        acc[i][j] = max3abs(acc[i][j], a, b);
-                        unpack2(sub2(xf[i].y, wf[j].y), a, b);
-                        acc[i][j] = max3abs(acc[i][j], a, b);
+                        linf_step(acc[i][j], xf[i], wf[j]);
+                    }
+                }
+            }
+            if (TRACK) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        if (acc[i][j] > prev[i][j])
+                            q[i][j >> 1] = (j & 1) ? __byte_perm(q[i][j >> 1], (uint32_t)kt, 0x5410)
+                                                   : __byte_perm(q[i][j >> 1], (uint32_t)kt, 0x3254);
+                        prev[i][j] = acc[i][j];
                     }
                 }
             }
@@ -346,19 +417,33 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
             for (int j = 0; j < 8; j++) {
                 const int n = n0 + wn * 64 + tj + 8 * j;
                 if (n >= p.CO) continue;
-                if (whole) p.y[(size_t)m * p.CO + n] = acc[i][j];
-                else atomic_max_nonneg(p.y + (size_t)m * p.CO + n, acc[i][j]);
+                const size_t o = (size_t)m * p.CO + n;
+                if (TRACK) {
+                    const uint32_t c = (j & 1) ? (q[i][j >> 1] >> 16) : (q[i][j >> 1] & 0xffffu);
+                    if (p.keys) {
+                        const unsigned long long key = pack_key(acc[i][j], c);
+                        if (whole) p.keys[o] = key;
+                        else atomicMax(p.keys + o, key);
+                    } else {
+                        p.y[o] = acc[i][j];
+                        p.pos[o] = c == 0xffffu ? -1 : (int)c;
+                    }
+                } else {
+                    if (whole) p.y[o] = acc[i][j];
+                    else atomic_max_nonneg(p.y + o, acc[i][j]);
+                }
             }
         }
         u0 += kb - ka;
     }
 }
 
-template <int WM, int WN, bool VEC>
-static cudaError_t launch_sk(InfSkParams p, cudaStream_t st) {
+// keys: 8 * B * CO bytes of scratch or null.  Without it a TRACK launch uses whole tiles only.
+template <int WM, int WN, bool VEC, bool TRACK>
+static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
     constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
-    auto kern = inf_fwd_sk_kernel<WM, WN, VEC>;
+    auto kern = inf_fwd_sk_kernel<WM, WN, VEC, TRACK>;
     static int ctas_per_sm[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -376,24 +461,30 @@ static cudaError_t launch_sk(InfSkParams p, cudaStream_t st) {
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const long long units = tiles * ((p.CI + BK - 1) / BK);
     long long grid = (long long)sm_count() * cps;
-    if (tiles % grid == 0 || units < grid) grid = tiles;  // whole tiles already balance
-    if (grid != tiles) {
-        cudaError_t e = cudaMemsetAsync(p.y, 0, sizeof(float) * (size_t)p.B * p.CO, st);
+    if (tiles % grid == 0 || units < grid || (TRACK && !p.keys)) grid = tiles;  // whole tiles
+    *split = (grid != tiles);
+    if (!*split) {
+        p.keys = nullptr;
+    } else {
+        cudaError_t e = TRACK ? cudaMemsetAsync(p.keys, 0, sizeof(unsigned long long) * (size_t)p.B * p.CO, st)
+                              : cudaMemsetAsync(p.y, 0, sizeof(float) * (size_t)p.B * p.CO, st);
         if (e != cudaSuccess) return e;
     }
     kern<<<(unsigned)grid, NT, SMEM, st>>>(p);
     return cudaGetLastError();
 }
 
-static cudaError_t dispatch_sk(const InfFwdParams& q, cudaStream_t st) {
-    InfSkParams p{q.x, q.w, q.y, q.B, q.CO, q.CI, 0, 0};
+// *split tells whether tiles were shared between CTAs; for TRACK that means the result is in
+// `keys` (workspace) and still has to be turned into y / pos by the resolve kernel.
+template <bool TRACK>
+static cudaError_t dispatch_sk(const InfFwdParams& q, unsigned long long* keys, bool* split, cudaStream_t st) {
+    InfSkParams p{q.x, q.w, q.y, q.pos, keys, q.B, q.CO, q.CI, 0, 0};
     const bool vec = (q.CI % 4 == 0) && aligned16(q.x) && aligned16(q.w);
     const long big = (long)((q.B + 63) / 64) * ((q.CO + 127) / 128);
-    if (big >= sm_count()) return vec ? launch_sk<2, 2, true>(p, st) : launch_sk<2, 2, false>(p, st);
-    return vec ? launch_sk<1, 2, true>(p, st) : launch_sk<1, 2, false>(p, st);
+    if (big >= sm_count())
+        return vec ? launch_sk<2, 2, true, TRACK>(p, split, st) : launch_sk<2, 2, false, TRACK>(p, split, st);
+    return vec ? launch_sk<1, 2, true, TRACK>(p, split, st) : launch_sk<1, 2, false, TRACK>(p, split, st);
 }
-
-// ---- host side ---------------------------------------------------------------------------
 
 template <int WM, int WN, int MODE, bool TRACK>
 struct FwdLaunch {
@@ -436,20 +527,9 @@ struct FwdLaunch {
     }
 };
 
-template <int MODE, bool TRACK>
-static cudaError_t dispatch_dense(const InfFwdParams& p, cudaStream_t st) {
-    cudaError_t err = cudaSuccess;
-    const double c4 = FwdLaunch<4, 2, MODE, TRACK>::cost(p, &err);
-    const double c2 = FwdLaunch<2, 2, MODE, TRACK>::cost(p, &err);
-    const double c1 = FwdLaunch<1, 2, MODE, TRACK>::cost(p, &err);
-    if (err != cudaSuccess) return err;
-    if (c4 <= c2 && c4 <= c1) return FwdLaunch<4, 2, MODE, TRACK>::launch(p, st);
-    if (c2 <= c1) return FwdLaunch<2, 2, MODE, TRACK>::launch(p, st);
-    return FwdLaunch<1, 2, MODE, TRACK>::launch(p, st);
-}
-
 template <bool TRACK>
-static cudaError_t dispatch_fwd(const InfFwdParams& p, cudaStream_t st) {
+static cudaError_t dispatch_fwd(const InfFwdParams& p, unsigned long long* keys, bool* split, cudaStream_t st) {
+    *split = false;
     if (p.ci || p.co) {
         cudaError_t err = cudaSuccess;
         const double c4 = FwdLaunch<1, 4, MODE_GATHER, TRACK>::cost(p, &err);
@@ -458,15 +538,14 @@ static cudaError_t dispatch_fwd(const InfFwdParams& p, cudaStream_t st) {
         return c4 <= c2 ? FwdLaunch<1, 4, MODE_GATHER, TRACK>::launch(p, st)
                         : FwdLaunch<1, 2, MODE_GATHER, TRACK>::launch(p, st);
     }
-    if (!TRACK) return dispatch_sk(p, st);
-    const bool vec = (p.CI % 4 == 0) && (p.W_CI % 4 == 0) && aligned16(p.x) && aligned16(p.w);
-    return vec ? dispatch_dense<MODE_VEC, TRACK>(p, st) : dispatch_dense<MODE_SCALAR, TRACK>(p, st);
+    return dispatch_sk<TRACK>(p, keys, split, st);
 }
 
 cudaError_t inf_forward_values(const float* x, const float* w, float* y, const int* ci, const int* co,
                                int B, int CO, int CI, int W_CI, cudaStream_t st) {
     InfFwdParams p{x, w, y, nullptr, ci, co, B, CO, CI, W_CI};
-    return dispatch_fwd<false>(p, st);
+    bool split = false;
+    return dispatch_fwd<false>(p, nullptr, &split, st);
 }
 
 }  // namespace snb
@@ -487,20 +566,45 @@ static int check_fwd(const void* x, const void* w, const void* y, int B, int CO,
     return SNB_OK;
 }
 
-extern "C" int snb_inf_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G,
-                                    int HW, float* y, int* pos, const int* w_index_ci,
-                                    const int* w_index_co, int W_CO, int W_CI, void* stream) {
-    int rc = check_fwd(x, w, y, B, CO, CI, G, HW, W_CO, W_CI, w_index_ci, w_index_co);
+static int inf_forward_impl(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                            float* y, int* pos, const int* ci, const int* co, int W_CO, int W_CI,
+                            unsigned long long* keys, cudaStream_t st) {
+    int rc = check_fwd(x, w, y, B, CO, CI, G, HW, W_CO, W_CI, ci, co);
     if (rc) return rc;
     if (!pos) return SNB_ERR_NULL_POINTER;
     if ((CI + CHUNK_TILES * BK - 1) / (CHUNK_TILES * BK) >= 0xffff) return SNB_ERR_TOO_LARGE;
-    cudaStream_t st = (cudaStream_t)stream;
-    InfFwdParams p{x, w, y, pos, w_index_ci, w_index_co, B, CO, CI, W_CI};
-    SNB_CUDA(dispatch_fwd<true>(p, st));
+    InfFwdParams p{x, w, y, pos, ci, co, B, CO, CI, W_CI};
+    bool split = false;
+    SNB_CUDA(dispatch_fwd<true>(p, keys, &split, st));
     dim3 grid((CO + 31) / 32, (B + 7) / 8);
-    inf_resolve_kernel<<<grid, 256, 0, st>>>(p);
+    if (split) inf_resolve_kernel<true><<<grid, 256, 0, st>>>(p, keys);
+    else inf_resolve_kernel<false><<<grid, 256, 0, st>>>(p, nullptr);
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
+}
+
+extern "C" int snb_inf_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G,
+                                    int HW, float* y, int* pos, const int* w_index_ci,
+                                    const int* w_index_co, int W_CO, int W_CI, void* stream) {
+    return inf_forward_impl(x, w, B, CO, CI, G, HW, y, pos, w_index_ci, w_index_co, W_CO, W_CI, nullptr,
+                            (cudaStream_t)stream);
+}
+
+extern "C" size_t snb_inf_dist_forward_workspace_bytes(int B, int CO) {
+    return (B > 0 && CO > 0) ? sizeof(unsigned long long) * (size_t)B * (size_t)CO : 0;
+}
+
+extern "C" int snb_inf_dist_forward_ws(const float* x, const float* w, int B, int CO, int CI, int G,
+                                       int HW, float* y, int* pos, const int* w_index_ci,
+                                       const int* w_index_co, int W_CO, int W_CI, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+    unsigned long long* keys = nullptr;
+    if (workspace) {
+        if (reinterpret_cast<uintptr_t>(workspace) & 7u) return SNB_ERR_ALIGNMENT;
+        if (workspace_bytes >= snb_inf_dist_forward_workspace_bytes(B, CO)) keys = (unsigned long long*)workspace;
+    }
+    return inf_forward_impl(x, w, B, CO, CI, G, HW, y, pos, w_index_ci, w_index_co, W_CO, W_CI, keys,
+                            (cudaStream_t)stream);
 }
 
 extern "C" int snb_inf_dist_forward_nograd(const float* x, const float* w, int B, int CO, int CI,
@@ -508,7 +612,8 @@ extern "C" int snb_inf_dist_forward_nograd(const float* x, const float* w, int B
     int rc = check_fwd(x, w, y, B, CO, CI, G, HW, CO, CI, nullptr, nullptr);
     if (rc) return rc;
     InfFwdParams p{x, w, y, nullptr, nullptr, nullptr, B, CO, CI, CI};
-    SNB_CUDA(dispatch_fwd<false>(p, (cudaStream_t)stream));
+    bool split = false;
+    SNB_CUDA(dispatch_fwd<false>(p, nullptr, &split, (cudaStream_t)stream));
     return SNB_OK;
 }
 

@@ -31,11 +31,12 @@ def test_library_exports_every_declared_symbol(built_lib):
 
 def test_loader_signatures_cover_the_header(built_lib):
     from sortnet_b200 import _lib
-    utility = {"snb_status_string", "snb_last_cuda_error", "snb_version"}
+    utility = {"snb_status_string", "snb_last_cuda_error", "snb_version", "snb_inf_dist_forward_workspace_bytes"}
     assert set(_lib.SIGNATURES) | utility == set(declared_symbols())
     lib = _lib.load()
     assert lib.snb_version() >= 100
     assert lib.snb_status_string(0) == b"ok" and b"null" in lib.snb_status_string(1)
+    assert lib.snb_inf_dist_forward_workspace_bytes(512, 5120) == 8 * 512 * 5120
 
 
 def test_status_codes_without_gpu(built_lib):

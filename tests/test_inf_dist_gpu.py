@@ -95,6 +95,34 @@ def test_masked_vs_oracle(B, CI, CO, keep, which):
     assert rel(gx, gx_o) < 1e-5 and rel(gw, gw_o) < 1e-5
 
 
+@pytest.mark.parametrize("B,CI,CO", [(128, 784, 5120), (512, 1024, 2100), (100, 130, 257)])
+def test_workspace_and_plain_entry_points_agree(B, CI, CO):
+    """Unmasked forward through the C ABI three ways: without scratch, with scratch (tiles split
+    along the reduction axis), with a too-small scratch (falls back).  All bit-identical."""
+    from sortnet_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(CO)
+    x = (rng.integers(0, 8, (B, CI)) / 8).astype(np.float32)      # plenty of exact ties
+    w = (rng.integers(-16, 17, (CO, CI)) / 8).astype(np.float32)
+    y_o, pos_o = oracle.inf_dist_forward(x, w)
+    X, W = col3(x), dev(w)
+    st = torch.cuda.current_stream().cuda_stream
+    need = lib.snb_inf_dist_forward_workspace_bytes(B, CO)
+    assert need == 8 * B * CO
+    for ws_bytes in (None, need, 64):
+        y = torch.zeros(B, CO, 1, device="cuda")
+        pos = torch.zeros(B, CO, 1, device="cuda", dtype=torch.int32)
+        if ws_bytes is None:
+            rc = lib.snb_inf_dist_forward(X.data_ptr(), W.data_ptr(), B, CO, CI, 1, 1, y.data_ptr(),
+                                          pos.data_ptr(), None, None, CO, CI, st)
+        else:
+            ws = torch.full((max(ws_bytes // 8, 1),), -1, dtype=torch.int64, device="cuda")
+            rc = lib.snb_inf_dist_forward_ws(X.data_ptr(), W.data_ptr(), B, CO, CI, 1, 1, y.data_ptr(),
+                                             pos.data_ptr(), None, None, CO, CI, ws.data_ptr(), ws_bytes, st)
+        assert rc == 0
+        assert np.array_equal(host(y), y_o) and np.array_equal(host(pos), pos_o)
+
+
 def test_ties_floor_and_sign():
     # quantised inputs force many exact ties: lowest index must win, sign from x - w
     rng = np.random.default_rng(7)
