@@ -41,6 +41,7 @@ extern "C" {
 #define SNB_STATUS_TOO_LARGE 4
 #define SNB_STATUS_CUDA 5
 #define SNB_STATUS_ALIGNMENT 6
+#define SNB_STATUS_STATIC_CAPACITY 7
 
 const char* snb_status_string(int status);
 const char* snb_last_cuda_error(void);
@@ -77,6 +78,28 @@ size_t snb_inf_dist_forward_workspace_bytes(int B, int CO);
 int snb_inf_dist_forward_ws(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
                             float* y, int* pos, const int* w_index_ci, const int* w_index_co,
                             int W_CO, int W_CI, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Unmasked snb_inf_dist_forward for callers that must not allocate device memory.  It has no
+ * counterpart in the reference.  Who needs it: a host that binds this C ABI directly — a C or C++
+ * serving loop, a plugin inside another runtime — has no tensor library to hand it cached scratch,
+ * and calling cudaMalloc / cudaFree around every forward is not an option for it: those calls
+ * synchronise the whole device, can fail when memory is fragmented or budgeted by the embedding
+ * application, and are forbidden in code paths that only enqueue work.  This variant runs the
+ * same k-split kernel as snb_inf_dist_forward_ws, but its merge scratch is an 8 MiB array that
+ * is part of the library image on every GPU that loads it; the function calls no allocator of
+ * any kind (no cudaMalloc, no cudaFree, no library routine that allocates).
+ *   - Limit: B * CO <= snb_inf_dist_forward_noalloc_max_outputs() = 1048576 (e.g. 128 x 5120);
+ *     larger problems return SNB_STATUS_STATIC_CAPACITY and must use the other two entry points.
+ *   - The first call on each device looks up the array's device address (a one-off set-up step
+ *     done with that device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array: the part a call uses is cleared on `stream`
+ *     before the kernel runs, and whatever the previous call left there is ignored, but two calls
+ *     whose GPU work overlaps in time (different streams, different host threads) race on it.
+ *     Serialise them, or give concurrent callers snb_inf_dist_forward_ws with their own scratch.
+ *   - Results are bit-identical to snb_inf_dist_forward. */
+int snb_inf_dist_forward_noalloc(const float* x, const float* w, int B, int CO, int CI, int G,
+                                 int HW, float* y, int* pos, void* stream);
+int snb_inf_dist_forward_noalloc_max_outputs(void);
 
 /* Same y without pos, unmasked.  Replaces inf_dist::forward_nograd (norm_dist.h:22-23;
  * inf_dist_cuda.cu:277-304). */

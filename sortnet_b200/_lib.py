@@ -16,6 +16,7 @@ _F = ctypes.c_float
 SIGNATURES = {
     "snb_inf_dist_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
     "snb_inf_dist_forward_ws": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, ctypes.c_size_t, _P],
+    "snb_inf_dist_forward_noalloc": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "snb_inf_dist_forward_nograd": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
     "snb_inf_dist_backward_input": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
     "snb_inf_dist_backward_input_weight": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
@@ -61,6 +62,8 @@ def load(build_if_missing: bool = False):
     lib.snb_last_cuda_error.restype = ctypes.c_char_p
     lib.snb_version.argtypes = []
     lib.snb_version.restype = ctypes.c_int
+    lib.snb_inf_dist_forward_noalloc_max_outputs.argtypes = []
+    lib.snb_inf_dist_forward_noalloc_max_outputs.restype = ctypes.c_int
     lib.snb_inf_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.snb_inf_dist_forward_workspace_bytes.restype = ctypes.c_size_t
     _lib = lib

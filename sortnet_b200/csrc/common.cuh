@@ -17,6 +17,7 @@ enum {
     SNB_ERR_TOO_LARGE = 4,        // an index would not fit 31 bits
     SNB_ERR_CUDA = 5,             // a CUDA runtime call failed (see snb_last_cuda_error)
     SNB_ERR_ALIGNMENT = 6,
+    SNB_ERR_STATIC_CAPACITY = 7,  // B * CO exceeds the built-in scratch of the no-allocation entry point
 };
 
 namespace snb {

@@ -617,6 +617,44 @@ extern "C" int snb_inf_dist_forward_nograd(const float* x, const float* w, int B
     return SNB_OK;
 }
 
+// ---- entry point that allocates nothing ----------------------------------------------------
+// Scratch for snb_inf_dist_forward_noalloc: one 64-bit merge key per output, held by every GPU
+// that loads this library until the process exits (8 MiB).
+#define SNB_NOALLOC_MAX_OUTPUTS (1 << 20)
+static __device__ __align__(256) unsigned long long snb_noalloc_keys[SNB_NOALLOC_MAX_OUTPUTS];
+
+// Device address of snb_noalloc_keys on the current device.  In host code the array's name is
+// only a handle for the runtime, not a pointer a kernel could use, so the address is looked up
+// once per device with that device current and cached.
+static cudaError_t noalloc_keys_address(unsigned long long** out) {
+    static unsigned long long* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, snb_noalloc_keys);
+        if (e != cudaSuccess) return e;
+        cached[dev] = static_cast<unsigned long long*>(ptr);
+    }
+    *out = cached[dev];
+    return cudaSuccess;
+}
+
+extern "C" int snb_inf_dist_forward_noalloc(const float* x, const float* w, int B, int CO, int CI,
+                                            int G, int HW, float* y, int* pos, void* stream) {
+    if (B > 0 && CO > 0 && (long long)B * CO > SNB_NOALLOC_MAX_OUTPUTS) return SNB_ERR_STATIC_CAPACITY;
+    unsigned long long* keys = nullptr;
+    SNB_CUDA(noalloc_keys_address(&keys));
+    // The launcher zero-fills the keys it is going to merge into (cudaMemsetAsync on `stream`)
+    // before the kernel runs, so what an earlier call left in the array does not matter.
+    return inf_forward_impl(x, w, B, CO, CI, G, HW, y, pos, nullptr, nullptr, CO, CI, keys,
+                            (cudaStream_t)stream);
+}
+
+extern "C" int snb_inf_dist_forward_noalloc_max_outputs(void) { return SNB_NOALLOC_MAX_OUTPUTS; }
+
 static int inf_backward(const float* g, const int* pos, int B, int CO, int CI, int G, int HW,
                         float* gx, float* gw, const int* ci, const int* co, int W_CO, int W_CI,
                         cudaStream_t st) {

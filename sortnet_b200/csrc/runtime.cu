@@ -32,6 +32,9 @@ extern "C" const char* snb_status_string(int status) {
         case SNB_ERR_TOO_LARGE: return "tensor too large for 31-bit indexing";
         case SNB_ERR_CUDA: return "CUDA runtime error";
         case SNB_ERR_ALIGNMENT: return "pointer not aligned to its element type";
+        case SNB_ERR_STATIC_CAPACITY:
+            return "B * CO exceeds the built-in scratch of snb_inf_dist_forward_noalloc (1048576 outputs); "
+                   "use snb_inf_dist_forward or snb_inf_dist_forward_ws";
         default: return "unknown status";
     }
 }
