@@ -170,6 +170,33 @@ int snb_bound_inf_dist_backward_input_weight(const float* grad_yl, const float* 
                                              int G, int HW, float* grad_xl, float* grad_xu,
                                              float* grad_w, void* stream);
 
+/* ---- sort neuron (evaluation-time form of the masked l-infinity neuron) -------------------- */
+
+/* y[b,j] = (1e-10 + sum_{r<K} q (1-q)^r * r-th largest |x[b,c] - w[j,c]|) / (1 - (1-q)^K),
+ * 2 <= K <= 25, 0 < q < 1.  Replaces sort_neuron::forward_nograd (norm_dist.h:48-49;
+ * sort_neuron.cu:403-435). */
+int snb_sort_neuron_forward_nograd(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                                   float* y, float q, int K, void* stream);
+
+/* Same value plus pos [K, B, CO, HW]: word of the r-th largest element (index | bit 31 when
+ * x - w < 0); of equal values the later index ranks higher; unfilled ranks hold word 0.
+ * Replaces sort_neuron::forward (norm_dist.h:50-51; sort_neuron.cu:453-485). */
+int snb_sort_neuron_forward(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                            float* y, int* pos, float q, int K, void* stream);
+
+/* Interval bounds of the sort neuron over the box [xL, xU].
+ * Replaces bound_sort_neuron_forward_cuda (norm_dist.h:58-59; sort_neuron.cu:502-534). */
+int snb_bound_sort_neuron_forward(const float* xl, const float* xu, const float* w, int B, int CO, int CI,
+                                  int G, int HW, float* yl, float* yu, float q, int K, void* stream);
+
+/* Sparse backward through the K recorded positions.  Replaces sort_neuron::backward_input and
+ * ::backward_input_weight (norm_dist.h:52-56; sort_neuron.cu:536-562). */
+int snb_sort_neuron_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI, int G,
+                                   int HW, float* grad_input, float q, int K, void* stream);
+int snb_sort_neuron_backward_input_weight(const float* grad_output, const int* pos, int B, int CO, int CI,
+                                          int G, int HW, float* grad_input, float* grad_weight, float q,
+                                          int K, void* stream);
+
 /* ---- mean shift ------------------------------------------------------------------------------ */
 
 /* mean[c] (c < C_full) = mean of x[b, slot(c)] over the rows whose sub-batch kept channel c

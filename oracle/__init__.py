@@ -170,3 +170,33 @@ def mean_shift_train_backward(gy, index, out_channels):
         sl = slice(s * SUB_BATCH, min(B, (s + 1) * SUB_BATCH))
         gx[sl] = gy[sl] - gmean[index[s]][None, :]
     return gx
+
+
+def sort_forward(x, w, q, K, want_pos=True):
+    """Sort neuron: y [B, CO], pos [K, B, CO] (rank 0 = largest) or None."""
+    x, w = _c32(x), _c32(w)
+    B, CI = x.shape
+    CO = w.shape[0]
+    y = np.empty((B, CO), np.float32)
+    pos = np.empty((K, B, CO), np.int32) if want_pos else None
+    lib().oracle_sort_forward(_f(x), _f(w), B, CO, CI, ctypes.c_float(q), K, _f(y), _i(pos))
+    return y, pos
+
+
+def sort_bound_forward(xl, xu, w, q, K):
+    xl, xu, w = _c32(xl), _c32(xu), _c32(w)
+    B, CI = xl.shape
+    CO = w.shape[0]
+    yl = np.empty((B, CO), np.float32)
+    yu = np.empty((B, CO), np.float32)
+    lib().oracle_sort_bound_forward(_f(xl), _f(xu), _f(w), B, CO, CI, ctypes.c_float(q), K, _f(yl), _f(yu))
+    return yl, yu
+
+
+def sort_backward(g, pos, CI, q, K, want_gw=True):
+    g, pos = _c32(g), _ci32(pos)
+    B, CO = g.shape
+    gx = np.empty((B, CI), np.float32)
+    gw = np.empty((CO, CI), np.float32) if want_gw else None
+    lib().oracle_sort_backward(_f(g), _i(pos), B, CO, CI, ctypes.c_float(q), K, _f(gx), _f(gw))
+    return gx, gw

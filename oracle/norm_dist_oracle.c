@@ -241,3 +241,103 @@ void oracle_norm_dist_backward(const float *g, const float *x, const float *w, c
         }
     }
 }
+
+/* Geometric weights of the sort neuron: rank r (0 = largest) gets q (1-q)^r, the sum is divided
+ * by 1 - (1-q)^K.  sort_neuron.cu:91-97 evaluates it in fp32 as below (no contraction here). */
+static float sort_combine(const float *res /* ascending, res[K-1] largest */, int K, float q, float eps0) {
+    float ans = eps0, c = 1.0f;
+    for (int k = K - 1; k >= 0; k--) {
+        ans += res[k] * c * q;
+        c *= 1 - q;
+    }
+    return ans / (1 - c);
+}
+
+/* Sort neuron forward.  sort_neuron.cu:16-102 (values: K-slot min/max insertion chain from
+ * zeros) and :115-214 (positions: a value enters only if it exceeds the smallest slot; it
+ * moves up past every slot it is >= to, so of equal values the later index ranks higher; slots
+ * never filled keep value 0 / word 0).  pos is [K][B][CO], rank 0 = largest; may be NULL. */
+void oracle_sort_forward(const float *x, const float *w, int B, int CO, int CI, float q, int K,
+                         float *y, int32_t *pos) {
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < B; b++) {
+        float res[32];
+        uint32_t idx[32];
+        for (int j = 0; j < CO; j++) {
+            for (int k = 0; k < K; k++) { res[k] = 0.f; idx[k] = 0; }
+            for (int c = 0; c < CI; c++) {
+                float t = x[(size_t)b * CI + c] - w[(size_t)j * CI + c];
+                float v = fabsf(t);
+                if (v > res[0]) {
+                    uint32_t word = (uint32_t)c | (t >= 0 ? 0u : SIGN_BIT);
+                    int k = 0;
+                    for (; k < K - 1; k++) {
+                        if (v < res[k + 1]) { res[k] = v; idx[k] = word; break; }
+                        res[k] = res[k + 1];
+                        idx[k] = idx[k + 1];
+                    }
+                    if (k == K - 1) { res[k] = v; idx[k] = word; }
+                }
+            }
+            y[(size_t)b * CO + j] = sort_combine(res, K, q, ORACLE_EPS);
+            if (pos)
+                for (int k = K - 1; k >= 0; k--)
+                    pos[(size_t)(K - 1 - k) * B * CO + (size_t)b * CO + j] = (int32_t)idx[k];
+        }
+    }
+}
+
+/* Interval bounds of the sort neuron.  sort_neuron.cu:216-314: bottom-K of min(t1, t2) and top-K of
+ * max(t1, t2) (t1 = w - xL, t2 = xU - w, inverted intervals repaired to the midpoint), both
+ * chains from zeros; yL = -(-EPS + sum)/(1 - (1-q)^K), yU = (EPS + sum)/(1 - (1-q)^K). */
+void oracle_sort_bound_forward(const float *xl, const float *xu, const float *w, int B, int CO,
+                               int CI, float q, int K, float *yl, float *yu) {
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < B; b++) {
+        float rl[32], ru[32];
+        for (int j = 0; j < CO; j++) {
+            for (int k = 0; k < K; k++) { rl[k] = 0.f; ru[k] = 0.f; }
+            for (int c = 0; c < CI; c++) {
+                float a = xl[(size_t)b * CI + c], d = xu[(size_t)b * CI + c];
+                if (a > d) { float m = (a + d) * 0.5f; a = m; d = m; }
+                float t1 = w[(size_t)j * CI + c] - a, t2 = d - w[(size_t)j * CI + c];
+                float vl = fminf(t1, t2), vu = fmaxf(t1, t2);
+                for (int k = 0; k < K - 1; k++) {
+                    rl[k] = fminf(rl[k], fmaxf(rl[k + 1], vl));
+                    ru[k] = fmaxf(ru[k], fminf(ru[k + 1], vu));
+                }
+                rl[K - 1] = fminf(rl[K - 1], vl);
+                ru[K - 1] = fmaxf(ru[K - 1], vu);
+            }
+            yl[(size_t)b * CO + j] = -sort_combine(rl, K, q, -ORACLE_EPS);
+            yu[(size_t)b * CO + j] = sort_combine(ru, K, q, ORACLE_EPS);
+        }
+    }
+}
+
+/* Sort neuron sparse backward.  sort_neuron.cu:316-375: rank r contributes
+ * (+/-) g * q (1-q)^r / (1 - (1-q)^K) to grad_x[b, idx_r] and its negation to grad_w[j, idx_r].
+ * Sums in double, rounded once.  gw may be NULL. */
+void oracle_sort_backward(const float *g, const int32_t *pos, int B, int CO, int CI, float q, int K,
+                          float *gx, float *gw) {
+    double *ax = (double *)calloc((size_t)B * CI, sizeof(double));
+    double *aw = gw ? (double *)calloc((size_t)CO * CI, sizeof(double)) : NULL;
+    float n = powf(1 - q, (float)K);
+    n = 1.0f + n / (1.0f - n);
+    for (int b = 0; b < B; b++)
+        for (int j = 0; j < CO; j++) {
+            float grad = g[(size_t)b * CO + j], c = n;
+            for (int k = 0; k < K; k++) {
+                uint32_t p = (uint32_t)pos[(size_t)k * B * CO + (size_t)b * CO + j];
+                int idx = (int)(p & ~SIGN_BIT);
+                float v = ((p & SIGN_BIT) ? -grad : grad) * c * q;
+                ax[(size_t)b * CI + idx] += v;
+                if (aw) aw[(size_t)j * CI + idx] -= v;
+                c *= 1 - q;
+            }
+        }
+    for (size_t i = 0; i < (size_t)B * CI; i++) gx[i] = (float)ax[i];
+    if (aw) for (size_t i = 0; i < (size_t)CO * CI; i++) gw[i] = (float)aw[i];
+    free(ax);
+    free(aw);
+}

@@ -27,6 +27,11 @@ SIGNATURES = {
     "snb_bound_inf_dist_forward": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
     "snb_bound_inf_dist_backward_input": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "snb_bound_inf_dist_backward_input_weight": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "snb_sort_neuron_forward_nograd": [_P, _P, _I, _I, _I, _I, _I, _P, _F, _I, _P],
+    "snb_sort_neuron_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _I, _P],
+    "snb_bound_sort_neuron_forward": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _I, _P],
+    "snb_sort_neuron_backward_input": [_P, _P, _I, _I, _I, _I, _I, _P, _F, _I, _P],
+    "snb_sort_neuron_backward_input_weight": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _I, _P],
     "snb_mean_shift_stats": [_P, _P, _I, _I, _I, _P, _P, _F, _P],
     "snb_mean_shift_apply": [_P, _P, _P, _I, _I, _P, _P],
     "snb_probe_fp32": [_P, _I, ctypes.POINTER(ctypes.c_double), _P],

@@ -1,0 +1,336 @@
+// Sort neuron: the deterministic, evaluation-time form of the masked l-infinity neuron.
+//   y[b,j] = (1e-10 + sum_{r<K} q (1-q)^r * (r-th largest |x[b,c] - w[j,c]|)) / (1 - (1-q)^K)
+// and its interval bounds, positions of the K largest elements, and the sparse backward.
+//
+// Replaces zbh2047/SortNet core/cuda/sort_neuron.cu (kernels :16-102, :115-214, :216-314, :316-375;
+// launchers :403-562).  K = min(CI, truncate) is 10 in every reference recipe; 2 <= K <= 25 is
+// accepted like there.  The values-only kernels keep a sorted K-slot list per output in
+// registers and insert with the min/max chain of the reference; they always carry 10 (or 25)
+// slots and use the top K of them, which is the same set.  The weighted sum is evaluated in
+// the reference's operation order; results agree with its kernels to fp32 rounding (the
+// reference binary may contract multiply-adds differently), positions agree exactly.
+#include "tile.cuh"
+#include "launch.h"
+
+namespace snb {
+
+struct SortParams {
+    const float* x;   // point value, or lower end of the box
+    const float* xu;  // upper end of the box (bounds only)
+    const float* w;
+    float* y;         // value, or lower bound
+    float* yu;        // upper bound (bounds only)
+    int* pos;         // [K][B][CO] or null
+    int B, CO, CI, K;
+    float q;
+};
+
+// ans = eps0 + sum over ranks, then / (1 - (1-q)^K); res ascending with res[KMAX-1] the largest.
+template <int KMAX>
+__device__ __forceinline__ float combine(const float (&res)[KMAX], int K, float q, float eps0) {
+    float ans = eps0, c = 1.0f;
+#pragma unroll
+    for (int r = 0; r < KMAX; r++) {
+        if (r < K) {
+            ans += res[KMAX - 1 - r] * c * q;
+            c *= 1 - q;
+        }
+    }
+    return ans / (1 - c);
+}
+
+// CTA of 256 threads, TM x TN outputs per thread (rows ty + 16 i, columns tx + 16 j): 4 x 4 for
+// up to 10 slots, 2 x 4 for up to 25; BOUND carries two chains per output (bottom-K of
+// min(t1,t2), top-K of max(t1,t2)) on TM x 2 outputs.
+template <int KMAX, bool BOUND>
+__global__ void __launch_bounds__(256) sort_fwd_kernel(const SortParams p) {
+    constexpr int TM = KMAX > 10 ? 2 : 4, TN = BOUND ? 2 : 4, BM = 16 * TM, BN = 16 * TN, NT = 256;
+    extern __shared__ __align__(16) float smem[];
+    float* xs = smem;                              // [2][BM][LDS]
+    float* us = xs + 2 * BM * LDS;                 // [2][BM][LDS] (BOUND)
+    float* ws = BOUND ? us + 2 * BM * LDS : us;    // [2][BN][LDS]
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int nk = (p.CI + BK - 1) / BK;
+    const bool vec = (p.CI % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.w) |
+                                          reinterpret_cast<uintptr_t>(p.xu)) & 15u) == 0;
+
+    auto stage = [&](int kt, int st) {
+        if (vec) {
+            stage_dense_vec<BM, NT>(xs + st * BM * LDS, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            if (BOUND) stage_dense_vec<BM, NT>(us + st * BM * LDS, p.xu, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            stage_dense_vec<BN, NT>(ws + st * BN * LDS, p.w, n0, p.CO, p.CI, kt * BK, p.CI, tid);
+        } else {
+            stage_dense_scalar<BM, NT>(xs + st * BM * LDS, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            if (BOUND) stage_dense_scalar<BM, NT>(us + st * BM * LDS, p.xu, m0, p.B, p.CI, kt * BK, p.CI, tid);
+            stage_dense_scalar<BN, NT>(ws + st * BN * LDS, p.w, n0, p.CO, p.CI, kt * BK, p.CI, tid);
+        }
+    };
+
+    float ru[TM][TN][KMAX];                      // top list (value kernel: the only list)
+    float rl[BOUND ? TM : 1][BOUND ? TN : 1][BOUND ? KMAX : 1];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++)
+#pragma unroll
+            for (int k = 0; k < KMAX; k++) {
+                ru[i][j][k] = 0.f;
+                if (BOUND) rl[i][j][k] = 0.f;
+            }
+
+    stage(0, 0);
+    cp_async_commit();
+    for (int kt = 0; kt < nk; kt++) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (kt + 1 < nk) stage(kt + 1, (kt + 1) & 1);
+        cp_async_commit();
+        if (BOUND) {  // midpoint repair of inverted intervals, in place
+            float* ld = xs + (kt & 1) * BM * LDS;
+            float* ud = us + (kt & 1) * BM * LDS;
+#pragma unroll
+            for (int r = 0; r < BM * BK / NT; r++) {
+                const int e = tid + r * NT, o = (e >> 5) * LDS + (e & 31);
+                const float a = ld[o], b = ud[o];
+                if (a > b) {
+                    const float m = (a + b) * 0.5f;
+                    ld[o] = m;
+                    ud[o] = m;
+                }
+            }
+            __syncthreads();
+        }
+        const float* xr = xs + (kt & 1) * BM * LDS + ty * LDS;
+        const float* ur = us + (kt & 1) * BM * LDS + ty * LDS;
+        const float* wr = ws + (kt & 1) * BN * LDS + tx * LDS;
+        // zero padding past CI or past the last row contributes |0 - 0| = 0 (resp. t1 = t2 = 0),
+        // which never changes a list that starts from zeros
+#pragma unroll 1
+        for (int k = 0; k < BK; k++) {
+            float xv[TM], uv[TM], wv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; i++) {
+                xv[i] = xr[i * 16 * LDS + k];
+                if (BOUND) uv[i] = ur[i * 16 * LDS + k];
+            }
+#pragma unroll
+            for (int j = 0; j < TN; j++) wv[j] = wr[j * 16 * LDS + k];
+#pragma unroll
+            for (int i = 0; i < TM; i++) {
+#pragma unroll
+                for (int j = 0; j < TN; j++) {
+                    if constexpr (BOUND) {
+                        const float t1 = wv[j] - xv[i], t2 = uv[i] - wv[j];
+                        const float vl = fminf(t1, t2), vu = fmaxf(t1, t2);
+#pragma unroll
+                        for (int s = 0; s < KMAX - 1; s++) {
+                            rl[i][j][s] = fminf(rl[i][j][s], fmaxf(rl[i][j][s + 1], vl));
+                            ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], vu));
+                        }
+                        rl[i][j][KMAX - 1] = fminf(rl[i][j][KMAX - 1], vl);
+                        ru[i][j][KMAX - 1] = fmaxf(ru[i][j][KMAX - 1], vu);
+                    } else {
+                        const float v = fabsf(xv[i] - wv[j]);
+#pragma unroll
+                        for (int s = 0; s < KMAX - 1; s++)
+                            ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], v));
+                        ru[i][j][KMAX - 1] = fmaxf(ru[i][j][KMAX - 1], v);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const int m = m0 + ty + 16 * i;
+        if (m >= p.B) continue;
+#pragma unroll
+        for (int j = 0; j < TN; j++) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= p.CO) continue;
+            const size_t o = (size_t)m * p.CO + n;
+            if constexpr (BOUND) {
+                p.y[o] = -combine<KMAX>(rl[i][j], p.K, p.q, -SNB_EPS);
+                p.yu[o] = combine<KMAX>(ru[i][j], p.K, p.q, SNB_EPS);
+            } else {
+                p.y[o] = combine<KMAX>(ru[i][j], p.K, p.q, SNB_EPS);
+            }
+        }
+    }
+}
+
+// Values and positions of the K largest elements: one thread per output, the sorted list lives in
+// shared memory ([slot][thread] so that neighbouring threads hit neighbouring banks).  A value
+// enters only when it beats the smallest slot; it then moves up past every slot it is >= to, so
+// among equal values the later index takes the higher rank, as in the reference.
+constexpr int SORT_POS_THREADS = 128;
+
+__global__ void __launch_bounds__(SORT_POS_THREADS) sort_fwd_pos_kernel(const SortParams p) {
+    extern __shared__ __align__(16) float smem[];
+    const int K = p.K;
+    float* res = smem;                                                    // [K][threads]
+    uint32_t* idx = reinterpret_cast<uint32_t*>(smem + K * SORT_POS_THREADS);  // [K][threads]
+    const int t = threadIdx.x;
+    const int n = blockIdx.x * SORT_POS_THREADS + t;
+    const int m = blockIdx.y;
+    for (int k = 0; k < K; k++) {
+        res[k * SORT_POS_THREADS + t] = 0.f;
+        idx[k * SORT_POS_THREADS + t] = 0u;
+    }
+    if (n >= p.CO) return;
+    const float* xr = p.x + (size_t)m * p.CI;
+    const float* wr = p.w + (size_t)n * p.CI;
+    float lowest = 0.f;
+    for (int c = 0; c < p.CI; c++) {
+        const float d = xr[c] - wr[c];
+        const float v = fabsf(d);
+        if (v > lowest) {
+            const uint32_t word = (uint32_t)c | (d >= 0 ? 0u : SNB_SIGN_BIT);
+            int k = 0;
+            for (; k < K - 1; k++) {
+                const float up = res[(k + 1) * SORT_POS_THREADS + t];
+                if (v < up) break;
+                res[k * SORT_POS_THREADS + t] = up;
+                idx[k * SORT_POS_THREADS + t] = idx[(k + 1) * SORT_POS_THREADS + t];
+            }
+            res[k * SORT_POS_THREADS + t] = v;
+            idx[k * SORT_POS_THREADS + t] = word;
+            lowest = res[t];
+        }
+    }
+    float ans = SNB_EPS, c = 1.0f;
+    const size_t o = (size_t)m * p.CO + n, plane = (size_t)p.B * p.CO;
+    for (int k = K - 1; k >= 0; k--) {
+        ans += res[k * SORT_POS_THREADS + t] * c * p.q;
+        c *= 1 - p.q;
+        p.pos[(size_t)(K - 1 - k) * plane + o] = (int)idx[k * SORT_POS_THREADS + t];
+    }
+    p.y[o] = ans / (1 - c);
+}
+
+// Sparse backward: one CTA per batch row, grad_x of the row accumulated in shared memory.
+__global__ void __launch_bounds__(256) sort_bwd_kernel(const float* __restrict__ g, const int* __restrict__ pos,
+                                                       int B, int CO, int CI, int K, float q, float c0,
+                                                       float* __restrict__ gx, float* __restrict__ gw,
+                                                       int use_smem) {
+    extern __shared__ float row[];
+    const int b = blockIdx.x;
+    float* acc = use_smem ? row : gx + (size_t)b * CI;
+    if (use_smem) {
+        for (int c = threadIdx.x; c < CI; c += blockDim.x) row[c] = 0.f;
+        __syncthreads();
+    }
+    const size_t plane = (size_t)B * CO;
+    for (int j = threadIdx.x; j < CO; j += blockDim.x) {
+        const size_t o = (size_t)b * CO + j;
+        const float grad = g[o];
+        float c = c0;
+        for (int k = 0; k < K; k++) {
+            const uint32_t pw = (uint32_t)pos[(size_t)k * plane + o];
+            const int i = (int)(pw & ~SNB_SIGN_BIT);
+            const float v = ((pw & SNB_SIGN_BIT) ? -grad : grad) * c * q;
+            atomicAdd(acc + i, v);
+            if (gw) atomicAdd(gw + (size_t)j * CI + i, -v);
+            c *= 1 - q;
+        }
+    }
+    if (use_smem) {
+        __syncthreads();
+        for (int c = threadIdx.x; c < CI; c += blockDim.x) gx[(size_t)b * CI + c] = row[c];
+    }
+}
+
+template <int KMAX, bool BOUND>
+static cudaError_t launch_sort_fwd(const SortParams& p, cudaStream_t st) {
+    constexpr int BM = KMAX > 10 ? 32 : 64, BN = BOUND ? 32 : 64;
+    constexpr int SMEM = 2 * ((BOUND ? 2 : 1) * BM + BN) * LDS * (int)sizeof(float);
+    auto kern = sort_fwd_kernel<KMAX, BOUND>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return e;
+        configured[dev & 63] = true;
+    }
+    dim3 grid((p.B + BM - 1) / BM, (p.CO + BN - 1) / BN);
+    kern<<<grid, 256, SMEM, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace snb
+
+using namespace snb;
+
+static int check_sort(const void* x, const void* w, const void* y, int B, int CO, int CI, int G, int HW,
+                      float q, int K) {
+    if (!x || !w || !y) return SNB_ERR_NULL_POINTER;
+    if (G != 1 || HW != 1 || K < 2 || K > 25 || !(q > 0.f) || !(q < 1.f)) return SNB_ERR_UNSUPPORTED;
+    if (B <= 0 || CO <= 0 || CI <= 0 || K > CI) return SNB_ERR_BAD_SHAPE;
+    if ((long long)CO * CI >= (1ll << 31) || (long long)B * CO * K >= (1ll << 31) || (long long)B * CI >= (1ll << 31))
+        return SNB_ERR_TOO_LARGE;
+    return SNB_OK;
+}
+
+extern "C" int snb_sort_neuron_forward_nograd(const float* x, const float* w, int B, int CO, int CI, int G,
+                                              int HW, float* y, float q, int K, void* stream) {
+    int rc = check_sort(x, w, y, B, CO, CI, G, HW, q, K);
+    if (rc) return rc;
+    SortParams p{x, x, w, y, nullptr, nullptr, B, CO, CI, K, q};
+    SNB_CUDA(K <= 10 ? launch_sort_fwd<10, false>(p, (cudaStream_t)stream)
+                     : launch_sort_fwd<25, false>(p, (cudaStream_t)stream));
+    return SNB_OK;
+}
+
+extern "C" int snb_sort_neuron_forward(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                                       float* y, int* pos, float q, int K, void* stream) {
+    int rc = check_sort(x, w, y, B, CO, CI, G, HW, q, K);
+    if (rc) return rc;
+    if (!pos) return SNB_ERR_NULL_POINTER;
+    SortParams p{x, x, w, y, nullptr, pos, B, CO, CI, K, q};
+    dim3 grid((CO + SORT_POS_THREADS - 1) / SORT_POS_THREADS, B);
+    sort_fwd_pos_kernel<<<grid, SORT_POS_THREADS, 2 * K * SORT_POS_THREADS * sizeof(float), (cudaStream_t)stream>>>(p);
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}
+
+extern "C" int snb_bound_sort_neuron_forward(const float* xl, const float* xu, const float* w, int B, int CO,
+                                             int CI, int G, int HW, float* yl, float* yu, float q, int K,
+                                             void* stream) {
+    int rc = check_sort(xl, w, yl, B, CO, CI, G, HW, q, K);
+    if (rc) return rc;
+    if (!xu || !yu) return SNB_ERR_NULL_POINTER;
+    SortParams p{xl, xu, w, yl, yu, nullptr, B, CO, CI, K, q};
+    SNB_CUDA(K <= 10 ? launch_sort_fwd<10, true>(p, (cudaStream_t)stream)
+                     : launch_sort_fwd<25, true>(p, (cudaStream_t)stream));
+    return SNB_OK;
+}
+
+static int sort_backward(const float* g, const int* pos, int B, int CO, int CI, int G, int HW, float* gx,
+                         float* gw, float q, int K, cudaStream_t st) {
+    if (!g || !pos || !gx) return SNB_ERR_NULL_POINTER;
+    if (G != 1 || HW != 1 || K < 2 || K > 25 || !(q > 0.f) || !(q < 1.f)) return SNB_ERR_UNSUPPORTED;
+    if (B <= 0 || CO <= 0 || CI <= 0) return SNB_ERR_BAD_SHAPE;
+    if ((long long)CO * CI >= (1ll << 31) || (long long)B * CO * K >= (1ll << 31)) return SNB_ERR_TOO_LARGE;
+    if (gw) SNB_CUDA(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)CO * CI, st));
+    const int use_smem = (size_t)CI * sizeof(float) <= 48 * 1024;
+    if (!use_smem) SNB_CUDA(cudaMemsetAsync(gx, 0, sizeof(float) * (size_t)B * CI, st));
+    float n = powf(1 - q, (float)K);
+    n = 1.0f + n / (1.0f - n);
+    sort_bwd_kernel<<<B, 256, use_smem ? CI * sizeof(float) : 0, st>>>(g, pos, B, CO, CI, K, q, n, gx, gw, use_smem);
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}
+
+extern "C" int snb_sort_neuron_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI,
+                                              int G, int HW, float* grad_input, float q, int K, void* stream) {
+    return sort_backward(grad_output, pos, B, CO, CI, G, HW, grad_input, nullptr, q, K, (cudaStream_t)stream);
+}
+
+extern "C" int snb_sort_neuron_backward_input_weight(const float* grad_output, const int* pos, int B, int CO,
+                                                     int CI, int G, int HW, float* grad_input,
+                                                     float* grad_weight, float q, int K, void* stream) {
+    if (!grad_weight) return SNB_ERR_NULL_POINTER;
+    return sort_backward(grad_output, pos, B, CO, CI, G, HW, grad_input, grad_weight, q, K, (cudaStream_t)stream);
+}

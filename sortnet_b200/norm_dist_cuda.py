@@ -51,6 +51,8 @@ _KERNELS = {
     "snb_norm_dist_backward_input_weight": 1, "snb_bound_inf_dist_forward_nograd": 1,
     "snb_bound_inf_dist_forward": 1, "snb_bound_inf_dist_backward_input": 1,
     "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1,
+    "snb_sort_neuron_forward_nograd": 1, "snb_sort_neuron_forward": 1, "snb_bound_sort_neuron_forward": 1,
+    "snb_sort_neuron_backward_input": 1, "snb_sort_neuron_backward_input_weight": 1,
 }
 
 launch_count = 0          # kernels launched through this module since import / reset_counters()
@@ -280,6 +282,66 @@ def bound_inf_dist_backward_input_weight(grad_outputL, grad_outputU, posL, posU,
     _call(dev, grad_outputL, "snb_bound_inf_dist_backward_input_weight", (B, CO, CI),
           _ptr(grad_outputL), _ptr(grad_outputU), _ptr(posL), _ptr(posU), B, CO, CI, G, HW,
           _ptr(grad_inputL), _ptr(grad_inputU), _ptr(grad_weight))
+
+
+def sort_neuron_forward(input, weight, output, pos, G, q, K):
+    """core/cuda/norm_dist.cpp:243-251.  pos: int32 [K, B, CO, HW]."""
+    _check(input, "input"); _check(weight, "weight"); _check(output, "output"); _check(pos, "pos", torch.int32)
+    B, CO, CI, HW = _dims(input, output)
+    if weight.size(0) != CO or weight.size(1) * G != CI or tuple(pos.shape) != (K, B, CO, HW):
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(input, weight, output, pos)
+    _call(dev, input, "snb_sort_neuron_forward", (B, CO, CI),
+          _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos), float(q), int(K))
+
+
+def bound_sort_neuron_forward(inputL, inputU, weight, outputL, outputU, G, q, K):
+    """core/cuda/norm_dist.cpp:253-263."""
+    for t, n in ((inputL, "inputL"), (inputU, "inputU"), (weight, "weight"), (outputL, "outputL"),
+                 (outputU, "outputU")):
+        _check(t, n)
+    B, CO, CI, HW = _dims(inputL, outputL)
+    if inputU.shape != inputL.shape or outputU.shape != outputL.shape or weight.size(0) != CO \
+            or weight.size(1) * G != CI:
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(inputL, inputU, weight, outputL, outputU)
+    _call(dev, inputL, "snb_bound_sort_neuron_forward", (B, CO, CI),
+          _ptr(inputL), _ptr(inputU), _ptr(weight), B, CO, CI, G, HW, _ptr(outputL), _ptr(outputU),
+          float(q), int(K))
+
+
+def sort_neuron_forward_nograd(input, weight, output, G, q, K):
+    """core/cuda/norm_dist.cpp:265-272."""
+    _check(input, "input"); _check(weight, "weight"); _check(output, "output")
+    B, CO, CI, HW = _dims(input, output)
+    if weight.size(0) != CO or weight.size(1) * G != CI:
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(input, weight, output)
+    _call(dev, input, "snb_sort_neuron_forward_nograd", (B, CO, CI),
+          _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), float(q), int(K))
+
+
+def sort_neuron_backward_input(grad_output, pos, grad_input, G, q, K):
+    """core/cuda/norm_dist.cpp:274-281."""
+    _check(grad_output, "grad_output"); _check(pos, "pos", torch.int32); _check(grad_input, "grad_input")
+    B, CO, CI, HW = grad_output.size(0), grad_output.size(1), grad_input.size(1), grad_input.size(2)
+    if tuple(pos.shape) != (K, B, CO, HW):
+        raise RuntimeError("pos must have shape [K, B, CO, HW]")
+    dev = _same_device(grad_output, pos, grad_input)
+    _call(dev, grad_output, "snb_sort_neuron_backward_input", (B, CO, CI),
+          _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), float(q), int(K))
+
+
+def sort_neuron_backward_input_weight(grad_output, pos, grad_input, grad_weight, G, q, K):
+    """core/cuda/norm_dist.cpp:283-292."""
+    _check(grad_output, "grad_output"); _check(pos, "pos", torch.int32)
+    _check(grad_input, "grad_input"); _check(grad_weight, "grad_weight")
+    B, CO, CI, HW = grad_output.size(0), grad_output.size(1), grad_input.size(1), grad_output.size(2)
+    if tuple(pos.shape) != (K, B, CO, HW) or grad_weight.size(0) != CO or grad_weight.size(1) * G != CI:
+        raise RuntimeError("shape mismatch")
+    dev = _same_device(grad_output, pos, grad_input, grad_weight)
+    _call(dev, grad_output, "snb_sort_neuron_backward_input_weight", (B, CO, CI),
+          _ptr(grad_output), _ptr(pos), B, CO, CI, G, HW, _ptr(grad_input), _ptr(grad_weight), float(q), int(K))
 
 
 def mean_shift_stats(x, index, mean, running_mean=None, momentum=0.1):

@@ -60,6 +60,8 @@ REFERENCE_NAMES = [
     "norm_dist_backward_input_weight", "inf_dist_forward", "inf_dist_forward_nograd",
     "inf_dist_backward_input", "inf_dist_backward_input_weight", "bound_inf_dist_forward",
     "bound_inf_dist_forward_nograd", "bound_inf_dist_backward_input", "bound_inf_dist_backward_input_weight",
+    "sort_neuron_forward", "bound_sort_neuron_forward", "sort_neuron_forward_nograd",
+    "sort_neuron_backward_input", "sort_neuron_backward_input_weight",
 ]
 
 

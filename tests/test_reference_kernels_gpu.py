@@ -124,3 +124,34 @@ def test_lp_close_to_the_reference_kernels(ref, p):
     torch.cuda.synchronize()
     assert (gx_r - gx_m).abs().max() <= 1e-3 * gx_r.abs().max()
     assert (gw_r - gw_m).abs().max() <= 1e-3 * gw_r.abs().max()
+
+
+@pytest.mark.parametrize("B,CI,CO,q,K", [(128, 784, 256, 0.9, 10), (70, 150, 90, 0.6, 10), (64, 300, 65, 0.5, 4)])
+def test_sort_neuron(ref, B, CI, CO, q, K):
+    from sortnet_b200 import norm_dist_cuda as C
+    x = torch.rand(B, CI, 1, device="cuda")
+    w = torch.randn(CO, CI, device="cuda")
+    y_r, y_m = torch.empty(B, CO, 1, device="cuda"), torch.empty(B, CO, 1, device="cuda")
+    ref.sort_neuron_forward_nograd(x, w, y_r, 1, q, K)
+    C.sort_neuron_forward_nograd(x, w, y_m, 1, q, K)
+    torch.cuda.synchronize()
+    assert ((y_r - y_m).abs() / y_r.abs()).max() < 2e-6
+    p_r = torch.empty(K, B, CO, 1, device="cuda", dtype=torch.int32)
+    p_m = torch.empty_like(p_r)
+    ref.sort_neuron_forward(x, w, y_r, p_r, 1, q, K)
+    C.sort_neuron_forward(x, w, y_m, p_m, 1, q, K)
+    torch.cuda.synchronize()
+    assert torch.equal(p_r, p_m) and ((y_r - y_m).abs() / y_r.abs()).max() < 2e-6
+    xl, xu = (x - 0.03).clamp(0, 1), (x + 0.03).clamp(0, 1)
+    l_r, u_r, l_m, u_m = (torch.empty(B, CO, 1, device="cuda") for _ in range(4))
+    ref.bound_sort_neuron_forward(xl, xu, w, l_r, u_r, 1, q, K)
+    C.bound_sort_neuron_forward(xl, xu, w, l_m, u_m, 1, q, K)
+    torch.cuda.synchronize()
+    assert ((l_r - l_m).abs() / l_r.abs()).max() < 2e-6 and ((u_r - u_m).abs() / u_r.abs()).max() < 2e-6
+    g = torch.randn(B, CO, 1, device="cuda")
+    gx_r, gw_r, gx_m, gw_m = torch.empty_like(x), torch.empty_like(w), torch.empty_like(x), torch.empty_like(w)
+    ref.sort_neuron_backward_input_weight(g, p_r, gx_r, gw_r, 1, q, K)
+    C.sort_neuron_backward_input_weight(g, p_m, gx_m, gw_m, 1, q, K)
+    torch.cuda.synchronize()
+    assert (gx_r - gx_m).abs().max() <= 1e-5 * gx_r.abs().max()
+    assert (gw_r - gw_m).abs().max() <= 1e-5 * gw_r.abs().max()
