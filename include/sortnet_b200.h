@@ -212,6 +212,15 @@ int snb_mean_shift_stats(const float* x, const int* index, int B, int C, int C_f
 int snb_mean_shift_apply(const float* x, const float* mean, const int* index, int B, int C,
                          float* y, void* stream);
 
+/* ---- optimiser ------------------------------------------------------------------------------- */
+
+/* One AdamW step over flat buffers of n fp32 values (n a multiple of 4, 16-byte aligned), with the
+ * arithmetic of torch.optim.AdamW; g is multiplied by grad_scale first; step counts from 1.
+ * Replaces the optimizer.step() of the reference's training loop (main.py:95,429-432), which is
+ * PyTorch code there. */
+int snb_adamw_step(float* w, const float* g, float* m, float* v, long long n, float lr, float beta1,
+                   float beta2, float eps, float weight_decay, int step, float grad_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,61 @@
+// Fused AdamW over one flat fp32 parameter buffer.
+//
+// The reference trains with torch.optim.AdamW over the model parameters (main.py:429-432, weight
+// decay 0 on the norm-distance weights) after DistributedDataParallel has averaged the gradients
+// (main.py:402).  Here parameters, gradients and both moments live in four flat buffers, so one
+// pass updates everything: 4 reads + 3 writes of 4 bytes per parameter, HBM-bound.
+// Arithmetic follows torch.optim.AdamW (decoupled weight decay, bias-corrected moments):
+//   w  *= 1 - lr * wd
+//   m   = b1 m + (1 - b1) g ;  v = b2 v + (1 - b2) g^2
+//   w  -= (lr / (1 - b1^t)) * m / (sqrt(v) / sqrt(1 - b2^t) + eps)
+// grad_scale multiplies g first (e.g. 1 / world size when the exchange summed the gradients).
+#include "common.cuh"
+#include "launch.h"
+
+namespace snb {
+
+__global__ void __launch_bounds__(256) adamw_kernel(float4* __restrict__ w, const float4* __restrict__ g,
+                                                    float4* __restrict__ m, float4* __restrict__ v, size_t n4,
+                                                    float decay, float b1, float b2, float step_size,
+                                                    float inv_sqrt_bc2, float eps, float grad_scale) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 wv = w[i], gv = g[i], mv = m[i], vv = v[i];
+        float* wp = reinterpret_cast<float*>(&wv);
+        const float* gp = reinterpret_cast<const float*>(&gv);
+        float* mp = reinterpret_cast<float*>(&mv);
+        float* vp = reinterpret_cast<float*>(&vv);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float gk = gp[k] * grad_scale;
+            mp[k] = b1 * mp[k] + (1.0f - b1) * gk;
+            vp[k] = b2 * vp[k] + (1.0f - b2) * gk * gk;
+            const float denom = sqrtf(vp[k]) * inv_sqrt_bc2 + eps;
+            wp[k] = wp[k] * decay - step_size * (mp[k] / denom);
+        }
+        w[i] = wv;
+        m[i] = mv;
+        v[i] = vv;
+    }
+}
+
+}  // namespace snb
+
+using namespace snb;
+
+extern "C" int snb_adamw_step(float* w, const float* g, float* m, float* v, long long n, float lr, float beta1,
+                              float beta2, float eps, float weight_decay, int step, float grad_scale,
+                              void* stream) {
+    if (!w || !g || !m || !v) return SNB_ERR_NULL_POINTER;
+    if (n <= 0 || step <= 0 || (n & 3)) return SNB_ERR_BAD_SHAPE;  // buffers are padded to 4 elements
+    if (!aligned16(w) || !aligned16(g) || !aligned16(m) || !aligned16(v)) return SNB_ERR_ALIGNMENT;
+    const double bc1 = 1.0 - pow((double)beta1, step), bc2 = 1.0 - pow((double)beta2, step);
+    const float step_size = (float)(lr / bc1), inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
+    const int blocks = sm_count() * 8;
+    adamw_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<float4*>(w), reinterpret_cast<const float4*>(g), reinterpret_cast<float4*>(m),
+        reinterpret_cast<float4*>(v), (size_t)n / 4, 1.0f - lr * weight_decay, beta1, beta2, step_size,
+        inv_sqrt_bc2, eps, grad_scale);
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}

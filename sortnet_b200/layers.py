@@ -27,11 +27,12 @@ from . import ops
 SUB_BATCH = 32
 
 
-def sample_mask(batch, groups, channel, q, device):
+def sample_mask(batch, groups, channel, q, device, count=None):
     """Kept-channel lists for `batch` sub-batches: one Binomial(channel, q) count shared by all
-    sub-batches, a uniformly random subset of that size per (sub-batch, group), sorted, int32,
-    shape [batch, groups, count]."""
-    count = int((torch.rand(channel, device=device) < q).sum().item())
+    sub-batches (drawn here unless the caller supplies it), a uniformly random subset of that
+    size per (sub-batch, group), sorted, int32, shape [batch, groups, count]."""
+    if count is None:
+        count = int((torch.rand(channel, device=device) < q).sum().item())
     scores = torch.rand(batch, groups, channel, device=device)
     picked = torch.topk(scores, k=count, dim=-1, sorted=False)[1].int()
     return torch.sort(picked)[0]
@@ -209,10 +210,20 @@ class SortMLPModel(nn.Module):
     def draw_masks(self, batch, device):
         """One kept-channel list per hidden activation (None where the next layer keeps all)."""
         sub = (batch - 1) // SUB_BATCH + 1
-        masks = []
-        for nxt in self.fc_dist[1:]:
-            q = nxt.keep_rate
-            masks.append(None if q == 1.0 else sample_mask(sub, 1, nxt.in_features, q, device))
+        todo = [(k, l) for k, l in enumerate(self.fc_dist[1:]) if l.keep_rate != 1.0]
+        masks = [None] * (len(self.fc_dist) - 1)
+        if not todo:
+            return masks
+        # all Binomial counts in one device round trip (one host synchronisation per step
+        # instead of one per layer)
+        width = max(l.in_features for _, l in todo)
+        u = torch.rand(len(todo), width, device=device)
+        keep = torch.tensor([l.keep_rate for _, l in todo], device=device).unsqueeze(1)
+        valid = torch.arange(width, device=device).unsqueeze(0) < torch.tensor(
+            [l.in_features for _, l in todo], device=device).unsqueeze(1)
+        counts = ((u < keep) & valid).sum(dim=1).tolist()
+        for (k, l), c in zip(todo, counts):
+            masks[k] = sample_mask(sub, 1, l.in_features, l.keep_rate, device, count=max(int(c), 1))
         return masks
 
     @torch.no_grad()

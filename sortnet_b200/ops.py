@@ -57,7 +57,10 @@ def _dist_backward(ctx, grad_y):
     x, weight, third = ctx.saved_tensors          # third = argmax words (p = inf) or y (finite p)
     ci, co = ctx.masks
     grad_x = torch.empty_like(x)
-    grad_w = torch.empty_like(weight) if need_w else None
+    # A weight that carries `grad_sink` (a tensor of its shape, see optim.FlatAdamW) gets its
+    # gradient written there and autograd receives None for it: nothing is copied or accumulated.
+    sink = getattr(weight, "grad_sink", None) if need_w else None
+    grad_w = (sink if sink is not None else torch.empty_like(weight)) if need_w else None
     if math.isinf(ctx.p):
         if need_w:
             _C.inf_dist_backward_input_weight(grad_y, third, grad_x, grad_w, ctx.group, ci, co)
@@ -68,7 +71,7 @@ def _dist_backward(ctx, grad_y):
             _C.norm_dist_backward_input_weight(grad_y, x, weight, third, grad_x, grad_w, ctx.group, ctx.p, ci, co)
         elif need_x:
             _C.norm_dist_backward_input(grad_y, x, weight, third, grad_x, ctx.group, ctx.p, ci, co)
-    return (grad_x if need_x else None), grad_w
+    return (grad_x if need_x else None), (None if sink is not None else grad_w)
 
 
 class NormDistF(torch.autograd.Function):

@@ -1,0 +1,65 @@
+"""Fused flat-buffer AdamW and the gradient sink against torch.optim.AdamW on the same model."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def loss_of(model, x, t, masks):
+    logits, margin = model(x, targets=t, eps=0.03, masks=masks)
+    return margin.clamp(min=0, max=1).max(dim=1)[0].mean() + 0.1 * F.cross_entropy(logits, t)
+
+
+@pytest.mark.parametrize("p_norm,wd", [(float("inf"), 0.0), (8.0, 0.02)])
+def test_flat_adamw_matches_torch_adamw(p_norm, wd):
+    from sortnet_b200.layers import SortMLPModel
+    from sortnet_b200.optim import FlatAdamW
+    torch.manual_seed(0)
+    ref = SortMLPModel(depth=4, width=96, input_dim=(3, 4, 4), num_classes=10, dropout=0.8, scalar=True).cuda()
+    ref.set_p(p_norm)
+    mine = copy.deepcopy(ref)
+    opt_ref = torch.optim.AdamW(ref.parameters(), lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=wd)
+    opt = FlatAdamW(mine, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=wd)
+    names = [n for n, _ in mine.named_parameters()]
+    for n, p in mine.named_parameters():
+        assert p.data_ptr() >= opt.flat_param.data_ptr() and hasattr(p, "grad_sink"), n
+    for step in range(3):
+        x = torch.rand(70, 3, 4, 4, device="cuda")
+        t = torch.randint(0, 10, (70,), device="cuda")
+        masks = ref.draw_masks(70, x.device)
+        opt_ref.zero_grad(set_to_none=True)
+        loss_of(ref.train(), x, t, masks).backward()
+        grads_ref = {n: p.grad.clone() for n, p in ref.named_parameters()}
+        opt_ref.step()
+        opt.zero_grad()
+        loss_of(mine.train(), x, t, masks).backward()
+        for n, p in mine.named_parameters():
+            if n.endswith("weight"):
+                assert p.grad is None, "weight gradients go to the sink, not through autograd"
+        opt.gather_grads()
+        for n, p in mine.named_parameters():
+            g = p.grad_sink
+            assert (g - grads_ref[n]).abs().max() <= 2e-5 * max(grads_ref[n].abs().max().item(), 1e-12), n
+            # Adam with eps = 1e-10 turns a gradient entry that cancels to exactly 0 in one summation
+            # order and to 1e-9 in another into updates of 0 and lr: compare the optimiser itself on
+            # identical gradients
+            g.copy_(grads_ref[n])
+        opt.step()
+        for (n, a), (_, b) in zip(ref.named_parameters(), mine.named_parameters()):
+            assert (a - b).abs().max() <= 1e-5 * max(a.abs().max().item(), 1.0), (step, n)
+    assert set(mine.state_dict().keys()) == set(ref.state_dict().keys()) and names
+
+
+def test_adamw_argument_checks():
+    from sortnet_b200 import _lib
+    lib = _lib.load()
+    buf = torch.zeros(16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    args = (buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr())
+    assert lib.snb_adamw_step(*args, 6, 0.1, 0.9, 0.99, 1e-8, 0.0, 1, 1.0, st) == 2      # not a multiple of 4
+    assert lib.snb_adamw_step(*args, 16, 0.1, 0.9, 0.99, 1e-8, 0.0, 0, 1.0, st) == 2     # steps count from 1
+    assert lib.snb_adamw_step(None, *args[1:], 16, 0.1, 0.9, 0.99, 1e-8, 0.0, 1, 1.0, st) == 1
+    assert lib.snb_adamw_step(buf.data_ptr() + 4, *args[1:], 12, 0.1, 0.9, 0.99, 1e-8, 0.0, 1, 1.0, st) == 6
