@@ -36,6 +36,15 @@ WORKLOAD = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (bound_fwd_kernel_512x5120x5120.md, inf_fwd_kernel_masked_512x4619x4596.md), at the
+# shapes of the widest layers of this workload.
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    "snb_bound_inf_dist_forward_nograd": 201.8e6,
+    "snb_inf_dist_forward": 120.4e6,
+}
+
+
 def layer_dims():
     pixels = WORKLOAD["input_dim"][0] * WORKLOAD["input_dim"][1] * WORKLOAD["input_dim"][2]
     w = WORKLOAD["width"]
@@ -345,7 +354,7 @@ def run_gpu_arm(args):
                 "bound": "fp32", "kernel": entry[4:], "shape_B_CO_CI": [b_, co_, ci_],
                 "ops_per_element": ops_per_elem, "ms_per_launch": round(mean_ms, 4),
                 "achieved": round(achieved, 1), "peak": round(peak_gflops, 1), "unit": "GFLOP/s",
-                "frac": round(achieved / peak_gflops, 4), "traffic": None,
+                "frac": round(achieved / peak_gflops, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(entry),
                 "peak_source": "FFMA probe timed in this run (2 flops per FMA); MEASURED_PEAKS.json has no FP32 "
                                "figure; nominal 148 SM x 128 lanes x 2 x 1.965 GHz = 74.5 TFLOP/s",
             }

@@ -124,15 +124,16 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams
 
     stage(0, 0);
     cp_async_commit();
+    if (MODE == MODE_GATHER && nk > 1) gw.fetch_cols(ci_s, BK, p.CI, tid);
 
     for (int kt = 0; kt < nk; kt++) {
         cp_async_wait<0>();
         __syncthreads();
         if (kt + 1 < nk) {
-            if (MODE == MODE_GATHER) {
-                gw.fetch_cols(ci_s, (kt + 1) * BK, p.CI, tid);
-            }
             stage(kt + 1, (kt + 1) & 1);
+            // kept-column indices of the tile after next: their load latency hides behind this
+            // tile's arithmetic instead of stalling the next staging step
+            if (MODE == MODE_GATHER && kt + 2 < nk) gw.fetch_cols(ci_s, (kt + 2) * BK, p.CI, tid);
         }
         cp_async_commit();
 

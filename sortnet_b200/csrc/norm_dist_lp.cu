@@ -158,12 +158,13 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
     const float skip_below = exp2f(-40.0f / p.p);
     stage(0, 0);
     cp_async_commit();
+    if (MODE == MODE_GATHER && nk > 1) gw.fetch_cols(ci_s, BK, p.CI, tid);
     for (int kt = 0; kt < nk; kt++) {
         cp_async_wait<0>();
         __syncthreads();
         if (kt + 1 < nk) {
-            if (MODE == MODE_GATHER) gw.fetch_cols(ci_s, (kt + 1) * BK, p.CI, tid);
             stage(kt + 1, (kt + 1) & 1);
+            if (MODE == MODE_GATHER && kt + 2 < nk) gw.fetch_cols(ci_s, (kt + 2) * BK, p.CI, tid);
         }
         cp_async_commit();
         const float* xr = xs + (kt & 1) * BM * LDS + tb * LDS;
