@@ -99,7 +99,8 @@ def config_block(n):
         "workload": "configs[1]: SortNet-MLP (5 x 5120 + head 10), CIFAR-shaped input [512, 3072] per GPU, "
                     "keep 0.9 sub-batch masks, p = inf, train eps 8/255, IBP eps 8/255",
         "global_batch": WORKLOAD["batch_per_gpu"] * n, "batch_per_gpu": WORKLOAD["batch_per_gpu"],
-        "parallelism": "dp%d" % n, "optimizer": "AdamW, fused flat-buffer kernel",
+        "parallelism": "dp%d" % n,
+        "optimizer": "AdamW, fused flat-buffer kernel" + (" with the gradient exchange over NVLink peer memory" if n > 1 else ""),
         "l2": "weights alone are 482 MB per step, larger than the 126 MB L2; no explicit flush",
     }
 
@@ -199,7 +200,10 @@ def run_gpu_arm(args):
     torch.manual_seed(1 + rank)  # masks and data differ per rank, like the reference's seed + rank
     # parameters, gradients and AdamW moments in flat buffers: one all-reduce, one fused update,
     # weight gradients written in place by the backward kernels
-    opt = FlatAdamW(model, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
+    # N > 1: gradient exchange and optimiser are one kernel over NVLink peer memory
+    # (SNB_PEER_STEP=0 falls back to one NCCL all-reduce followed by the local fused AdamW)
+    peer_step = world > 1 and os.environ.get("SNB_PEER_STEP", "1") != "0"
+    opt = FlatAdamW(model, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, peer_memory=peer_step)
 
     pool = 4
     gen = torch.Generator().manual_seed(100 + rank)

@@ -221,6 +221,16 @@ int snb_mean_shift_apply(const float* x, const float* mean, const int* index, in
 int snb_adamw_step(float* w, const float* g, float* m, float* v, long long n, float lr, float beta1,
                    float beta2, float eps, float weight_decay, int step, float grad_scale, void* stream);
 
+/* Data-parallel AdamW step fused with the gradient exchange: this rank sums elements [lo, hi) of
+ * the flat gradient buffers of all `world` ranks (peer pointers of one NVLink node, entry `rank`
+ * its own), divides by world, applies AdamW with its shard-sized moments m, v and stores the new
+ * parameter values into every rank's flat parameter buffer.  lo, hi multiples of 4; all pointers
+ * 16-byte aligned; world <= 16.  The caller orders ranks with barriers before and after.
+ * Replaces DistributedDataParallel's all-reduce plus optimizer.step() (main.py:402,95). */
+int snb_dp_adamw_step(const void* const* grad_ptrs, void* const* param_ptrs, float* m, float* v, int rank,
+                      int world, long long lo, long long hi, float lr, float beta1, float beta2, float eps,
+                      float weight_decay, int step, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

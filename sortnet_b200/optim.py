@@ -20,6 +20,16 @@ def _pad4(n):
     return (n + 3) // 4 * 4
 
 
+def shard_bounds(numel, world, rank):
+    """[lo, hi) of rank's shard of a flat buffer of `numel` (multiple of 4) elements; every bound
+    is a multiple of 4 and the shards tile the buffer."""
+    quads = numel // 4
+    per = (quads + world - 1) // world
+    lo = min(rank * per, quads)
+    hi = min(lo + per, quads)
+    return lo * 4, hi * 4
+
+
 class FlatAdamW:
     """AdamW over all parameters of `module` held in flat buffers.
 
@@ -31,7 +41,12 @@ class FlatAdamW:
     (the reference uses 0 for every norm-distance weight).
     """
 
-    def __init__(self, module, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, process_group=None):
+    def __init__(self, module, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, process_group=None,
+                 peer_memory=False):
+        """peer_memory=True (ranks of one NVLink node): the flat gradient and parameter buffers are
+        allocated as symmetric memory and `step()` runs the fused reduce-scatter + AdamW +
+        all-gather kernel over peer pointers instead of an NCCL all-reduce plus a local update;
+        each rank then keeps AdamW moments for its 1/world shard only."""
         self.params = [p for p in module.parameters() if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")
@@ -45,10 +60,30 @@ class FlatAdamW:
             offsets.append(total)
             total += _pad4(p.numel())          # every slice starts 16-byte aligned
         self.numel = total
-        self.flat_param = torch.zeros(total, device=dev, dtype=torch.float32)
-        self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
-        self.exp_avg = torch.zeros(total, device=dev, dtype=torch.float32)
-        self.exp_avg_sq = torch.zeros(total, device=dev, dtype=torch.float32)
+        self.peer = bool(peer_memory) and self.world > 1
+        if self.peer:
+            import ctypes
+            import torch.distributed._symmetric_memory as symm_mem
+            group = process_group if process_group is not None else dist.group.WORLD
+            self.flat_param = symm_mem.empty(total, dtype=torch.float32, device=dev)
+            self.flat_grad = symm_mem.empty(total, dtype=torch.float32, device=dev)
+            self.flat_param.zero_()
+            self.flat_grad.zero_()
+            self._hdl_param = symm_mem.rendezvous(self.flat_param, group)
+            self._hdl_grad = symm_mem.rendezvous(self.flat_grad, group)
+            self.rank = self._hdl_grad.rank
+            assert self._hdl_grad.world_size == self.world
+            arr = ctypes.c_void_p * self.world
+            self._grad_ptrs = arr(*[int(q) for q in self._hdl_grad.buffer_ptrs])
+            self._param_ptrs = arr(*[int(q) for q in self._hdl_param.buffer_ptrs])
+            self.lo, self.hi = shard_bounds(total, self.world, self.rank)
+            moments = max(self.hi - self.lo, 4)
+        else:
+            self.flat_param = torch.zeros(total, device=dev, dtype=torch.float32)
+            self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
+            moments = total
+        self.exp_avg = torch.zeros(moments, device=dev, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(moments, device=dev, dtype=torch.float32)
         self._slices = []
         for p, off in zip(self.params, offsets):
             view = self.flat_param[off:off + p.numel()].view_as(p)
@@ -73,13 +108,27 @@ class FlatAdamW:
 
     def all_reduce(self, async_op=False):
         """Sums the flat gradient over ranks (one collective); the mean is taken inside step()."""
-        if self.world == 1:
-            return None
+        if self.world == 1 or self.peer:
+            return None            # with peer memory the exchange is part of step()
         return dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
 
     def step(self):
         self.step_count += 1
         dev = self.flat_param.device
+        if self.peer:
+            with torch.cuda.device(dev):
+                st = torch.cuda.current_stream(dev).cuda_stream
+                # every rank's backward has finished writing its gradients ...
+                self._hdl_grad.barrier(channel=0, timeout_ms=60000)
+                rc = _lib.load().snb_dp_adamw_step(
+                    self._grad_ptrs, self._param_ptrs, self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                    self.rank, self.world, self.lo, self.hi, float(self.lr), float(self.betas[0]),
+                    float(self.betas[1]), float(self.eps), float(self.weight_decay), self.step_count, st)
+                # ... and every rank's new parameters have landed here before the next forward
+                self._hdl_param.barrier(channel=0, timeout_ms=60000)
+            _lib.check(rc, "dp_adamw_step")
+            _C.launch_count += 1
+            return
         with torch.cuda.device(dev):
             rc = _lib.load().snb_adamw_step(
                 self.flat_param.data_ptr(), self.flat_grad.data_ptr(), self.exp_avg.data_ptr(),
