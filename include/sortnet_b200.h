@@ -47,6 +47,11 @@ const char* snb_status_string(int status);
 const char* snb_last_cuda_error(void);
 int snb_version(void);
 
+/* 1 if a bounded device-side wait (the mbarrier waits of the TMA-staged kernels) ever gave up on the
+ * current device, 0 if not, -1 on a CUDA error; synchronises the device.  No counterpart in the
+ * reference. */
+int snb_device_wait_failed(void);
+
 /* Runs a register-only FMA chain (no counterpart in the reference); *flops = operations done.
  * The benchmark times it to get the FP32 CUDA-core peak used in its roofline fractions.
  * scratch: at least 4 bytes of device memory. */

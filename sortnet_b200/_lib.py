@@ -69,6 +69,8 @@ def load(build_if_missing: bool = False):
     lib.snb_last_cuda_error.restype = ctypes.c_char_p
     lib.snb_version.argtypes = []
     lib.snb_version.restype = ctypes.c_int
+    lib.snb_device_wait_failed.argtypes = []
+    lib.snb_device_wait_failed.restype = ctypes.c_int
     lib.snb_inf_dist_forward_noalloc_max_outputs.argtypes = []
     lib.snb_inf_dist_forward_noalloc_max_outputs.restype = ctypes.c_int
     lib.snb_inf_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int]

@@ -8,10 +8,15 @@
 // bit for bit.  The word variant records the first c (strict comparisons, ascending c) that
 // set each bound, bit 31 = (t1 > t2); posL = 0xffffffff when the lower bound never left
 // its floor.
+#include <stdlib.h>
 #include "tile.cuh"
 #include "launch.h"
 
 namespace snb {
+
+// bound_tma.cu: TMA-staged kernel for large aligned problems; cudaErrorNotSupported = not applicable
+cudaError_t bound_forward_tma(const float* xl, const float* xu, const float* w, float* yl, float* yu, int B, int CO,
+                              int CI, cudaStream_t st);
 
 struct BoundParams {
     const float* xl;
@@ -329,6 +334,16 @@ static cudaError_t launch_bound(BoundParams p, cudaStream_t st) {
 
 using namespace snb;
 
+// SNB_DISABLE_TMA=1 in the environment keeps the cp.async staging everywhere.
+static bool tma_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("SNB_DISABLE_TMA");
+        cached = (e && e[0] == '1') ? 0 : 1;
+    }
+    return cached == 1;
+}
+
 static int check_bound(const void* xl, const void* xu, const void* w, const void* yl, const void* yu,
                        int B, int CO, int CI, int G, int HW) {
     if (!xl || !xu || !w || !yl || !yu) return SNB_ERR_NULL_POINTER;
@@ -348,6 +363,11 @@ extern "C" int snb_bound_inf_dist_forward_nograd(const float* xl, const float* x
     const bool vec = (CI % 4 == 0) && aligned16(xl) && aligned16(xu) && aligned16(w);
     cudaStream_t st = (cudaStream_t)stream;
     const long big = (long)((B + 127) / 128) * ((CO + 127) / 128);
+    if (big >= sm_count() / 2 && tma_enabled()) {
+        cudaError_t e = bound_forward_tma(xl, xu, w, yl, yu, B, CO, CI, st);
+        if (e == cudaSuccess) return SNB_OK;
+        if (e != cudaErrorNotSupported) SNB_CUDA(e);
+    }
     if (big >= sm_count() / 2) {
         SNB_CUDA(vec ? launch_bound<4, 2, true>(p, st) : launch_bound<4, 2, false>(p, st));
     } else {

@@ -113,3 +113,21 @@ def test_bounds_enclose_the_point_value():
     # degenerate box reproduces the point value exactly
     yl0, yu0 = run_nograd(x, x, w)
     assert np.array_equal(yu0, y) and np.array_equal(yl0, y)
+
+
+@pytest.mark.parametrize("B,CI,CO", [(512, 1024, 2600), (500, 1028, 2500), (130, 2048, 9600)])
+def test_large_aligned_shapes_take_the_tma_path(B, CI, CO):
+    """Shapes big enough for the TMA-staged kernel (ragged rows, CI not a multiple of the k-tile,
+    some inverted intervals); results must still be bit-identical and no device wait may time out."""
+    from sortnet_b200 import _lib
+    rng = np.random.default_rng(B + CO)
+    x = rng.random((B, CI), dtype=np.float32)
+    xl = np.clip(x - np.float32(0.05), 0, 1).astype(np.float32)
+    xu = np.clip(x + np.float32(0.05), 0, 1).astype(np.float32)
+    flip = rng.random((B, CI)) < 0.01
+    xl[flip], xu[flip] = xu[flip] + np.float32(0.1), xl[flip]
+    w = rng.standard_normal((CO, CI)).astype(np.float32)
+    yl_o, yu_o, _, _ = oracle.bound_inf_dist_forward(xl, xu, w, want_pos=False)
+    yl, yu = run_nograd(xl, xu, w)
+    assert np.array_equal(yl, yl_o) and np.array_equal(yu, yu_o)
+    assert _lib.load().snb_device_wait_failed() == 0
