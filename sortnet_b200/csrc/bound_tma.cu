@@ -56,7 +56,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-constexpr int TMA_BM = 128, TMA_BN = 128, TMA_NT = 256, TMA_STAGES = 4;
+#ifndef SNB_TMA_TN
+#define SNB_TMA_TN 8
+#endif
+constexpr int TMA_TN = SNB_TMA_TN;                                // output columns per thread (8 or 4)
+constexpr int TMA_BM = 128, TMA_BN = 128, TMA_NT = 256 * 8 / TMA_TN, TMA_STAGES = 4;
 constexpr int TMA_TILE_FLOATS = 128 * BK;                         // 16 KiB
 constexpr int TMA_STAGE_FLOATS = 3 * TMA_TILE_FLOATS;             // x_L, x_U, W
 constexpr int TMA_SMEM = TMA_STAGES * TMA_STAGE_FLOATS * 4 + 1024 /*alignment slack*/ + 64 /*barriers*/;
@@ -80,7 +84,8 @@ __global__ void __launch_bounds__(TMA_NT) bound_fwd_tma_kernel(const __grid_cons
     float* tiles = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TMA_STAGES * TMA_STAGE_FLOATS);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wm = warp >> 1, wn = warp & 1, tb = lane >> 3, tj = lane & 7;
+    constexpr int WN = TMA_BN / (8 * TMA_TN);   // warps along the columns
+    const int wm = warp / WN, wn = warp % WN, tb = lane >> 3, tj = lane & 7;
 
     __shared__ int abort_flag;
     if (tid == 0) {
@@ -114,11 +119,11 @@ __global__ void __launch_bounds__(TMA_NT) bound_fwd_tma_kernel(const __grid_cons
             issued++;
         };
 
-        float accl[8][8], accu[8][8];
+        float accl[8][TMA_TN], accu[8][TMA_TN];
 #pragma unroll
         for (int i = 0; i < 8; i++)
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < TMA_TN; j++) {
                 accl[i][j] = -SNB_EPS;
                 accu[i][j] = SNB_EPS;
             }
@@ -158,7 +163,7 @@ __global__ void __launch_bounds__(TMA_NT) bound_fwd_tma_kernel(const __grid_cons
             }
 #pragma unroll 4
             for (int kk = 0; kk < BK / 2; kk++) {
-                float2 lf[8], uf[8], wf[8];
+                float2 lf[8], uf[8], wf[TMA_TN];
                 const int chunk = kk >> 1, within = (kk & 1) * 2;
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -167,12 +172,12 @@ __global__ void __launch_bounds__(TMA_NT) bound_fwd_tma_kernel(const __grid_cons
                     uf[i] = *reinterpret_cast<const float2*>(ut + o);
                 }
 #pragma unroll
-                for (int j = 0; j < 8; j++)
-                    wf[j] = *reinterpret_cast<const float2*>(wt + swz(wn * 64 + tj + 8 * j, chunk) + within);
+                for (int j = 0; j < TMA_TN; j++)
+                    wf[j] = *reinterpret_cast<const float2*>(wt + swz(wn * 8 * TMA_TN + tj + 8 * j, chunk) + within);
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
+                    for (int j = 0; j < TMA_TN; j++) {
                         float t1 = wf[j].x - lf[i].x, t2 = uf[i].x - wf[j].x;
                         accl[i][j] = min3(accl[i][j], t1, t2);
                         accu[i][j] = max3(accu[i][j], t1, t2);
@@ -190,8 +195,8 @@ __global__ void __launch_bounds__(TMA_NT) bound_fwd_tma_kernel(const __grid_cons
             const int m = m0 + wm * 32 + tb + 4 * i;
             if (m >= p.B) continue;
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int n = n0 + wn * 64 + tj + 8 * j;
+            for (int j = 0; j < TMA_TN; j++) {
+                const int n = n0 + wn * 8 * TMA_TN + tj + 8 * j;
                 if (n >= p.CO) continue;
                 const size_t o = (size_t)m * p.CO + n;
                 if (whole) {

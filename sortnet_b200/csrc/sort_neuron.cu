@@ -123,19 +123,29 @@ __global__ void __launch_bounds__(256) sort_fwd_kernel(const SortParams p) {
                     if constexpr (BOUND) {
                         const float t1 = wv[j] - xv[i], t2 = uv[i] - wv[j];
                         const float vl = fminf(t1, t2), vu = fmaxf(t1, t2);
+                        // A value that does not beat the weakest slot leaves the whole list
+                        // unchanged, so the chain is only walked when some lane needs it (after the
+                        // first few hundred columns that is a minority of the steps).
+                        if (vl < rl[i][j][0]) {
 #pragma unroll
-                        for (int s = 0; s < KMAX - 1; s++) {
-                            rl[i][j][s] = fminf(rl[i][j][s], fmaxf(rl[i][j][s + 1], vl));
-                            ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], vu));
+                            for (int s = 0; s < KMAX - 1; s++)
+                                rl[i][j][s] = fminf(rl[i][j][s], fmaxf(rl[i][j][s + 1], vl));
+                            rl[i][j][KMAX - 1] = fminf(rl[i][j][KMAX - 1], vl);
                         }
-                        rl[i][j][KMAX - 1] = fminf(rl[i][j][KMAX - 1], vl);
-                        ru[i][j][KMAX - 1] = fmaxf(ru[i][j][KMAX - 1], vu);
+                        if (vu > ru[i][j][0]) {
+#pragma unroll
+                            for (int s = 0; s < KMAX - 1; s++)
+                                ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], vu));
+                            ru[i][j][KMAX - 1] = fmaxf(ru[i][j][KMAX - 1], vu);
+                        }
                     } else {
                         const float v = fabsf(xv[i] - wv[j]);
+                        if (v > ru[i][j][0]) {
 #pragma unroll
-                        for (int s = 0; s < KMAX - 1; s++)
-                            ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], v));
-                        ru[i][j][KMAX - 1] = fmaxf(ru[i][j][KMAX - 1], v);
+                            for (int s = 0; s < KMAX - 1; s++)
+                                ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], v));
+                            ru[i][j][KMAX - 1] = fmaxf(ru[i][j][KMAX - 1], v);
+                        }
                     }
                 }
             }
