@@ -41,7 +41,7 @@ WORKLOAD = {
 # shapes of the widest layers of this workload.
 NCU_DRAM_BYTES_PER_LAUNCH = {
     "snb_bound_inf_dist_forward_nograd": 201.8e6,
-    "snb_inf_dist_forward": 120.4e6,
+    "snb_inf_dist_forward_ws": 120.4e6,
 }
 
 
@@ -335,11 +335,19 @@ def run_gpu_arm(args):
         peak_gflops = best * 1e-9
 
         def kernel_stats(entry):
-            rows = {k: v for k, v in timeline.items() if k[0] == entry}
+            """Launches of `entry` on the widest layers (mask sizes differ a little from step to
+            step, so every shape within 10 % of the largest counts): a representative shape, the
+            mean time per launch and the mean element count per launch."""
+            rows = {k[1]: v for k, v in timeline.items() if k[0] == entry}
             if not rows:
                 return None
-            tag = max(rows, key=lambda k: sum(rows[k]))       # the shape that took the most time
-            return tag[1], statistics.mean(rows[tag]), sum(sum(v) for v in rows.values())
+            size = lambda t: t[0] * t[1] * t[2]
+            biggest = max(size(t) for t in rows)
+            picked = {t: v for t, v in rows.items() if size(t) >= 0.9 * biggest}
+            launches = sum(len(v) for v in picked.values())
+            total_ms = sum(sum(v) for v in picked.values())
+            elems = sum(size(t) * len(v) for t, v in picked.items()) / launches
+            return max(picked, key=size), total_ms / launches, elems
 
         by_entry = {}
         for (entry, tag), v in timeline.items():
@@ -348,12 +356,12 @@ def run_gpu_arm(args):
         shares = {k[4:]: round(v / total_kernel_ms, 4) for k, v in sorted(by_entry.items(), key=lambda kv: -kv[1])}
 
         roofs = {}
-        for entry, ops_per_elem in (("snb_bound_inf_dist_forward_nograd", 6.0), ("snb_inf_dist_forward", 2.0)):
+        for entry, ops_per_elem in (("snb_bound_inf_dist_forward_nograd", 6.0), ("snb_inf_dist_forward_ws", 2.0)):
             ks = kernel_stats(entry)
             if ks is None:
                 continue
-            (b_, co_, ci_), mean_ms, _ = ks
-            achieved = ops_per_elem * b_ * co_ * ci_ / (mean_ms * 1e-3) * 1e-9
+            (b_, co_, ci_), mean_ms, mean_elems = ks
+            achieved = ops_per_elem * mean_elems / (mean_ms * 1e-3) * 1e-9
             roofs[entry] = {
                 "bound": "fp32", "kernel": entry[4:], "shape_B_CO_CI": [b_, co_, ci_],
                 "ops_per_element": ops_per_elem, "ms_per_launch": round(mean_ms, 4),
@@ -377,11 +385,11 @@ def run_gpu_arm(args):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": dominant,
-            "roofline_linf_forward": roofs.get("snb_inf_dist_forward"),
+            "roofline_linf_forward": roofs.get("snb_inf_dist_forward_ws"),
             "kernel_time_share": shares,
             "kernel_ms_per_step": round(total_kernel_ms / args.steps, 3),
         }
-        if world == 1:
+        if world == 1 and not args.no_lp:
             # the p-annealed phases of the recipe (p = 8, then a general p) on the same model: one
             # masked training step without the bound pass, device-timed, reported beside the headline
             lp = {}
@@ -433,6 +441,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-lp", action="store_true", help="skip the p = 8 / p = 31.6 training-step extras")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

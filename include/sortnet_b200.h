@@ -71,10 +71,10 @@ int snb_inf_dist_forward(const float* x, const float* w, int B, int CO, int CI, 
                          float* y, int* pos, const int* w_index_ci, const int* w_index_co,
                          int W_CO, int W_CI, void* stream);
 
-/* The same operation with caller-provided scratch memory.  Without masks the kernel can then
- * share output tiles between thread blocks along the reduction axis (every SM gets the same
- * amount of work whatever the shape) and merge the partial (value, position) pairs with 64-bit
- * atomics in `workspace`; with masks, or when workspace is NULL / smaller than
+/* The same operation with caller-provided scratch memory.  The kernel can then share output
+ * tiles between thread blocks along the reduction axis (every SM gets the same amount of work
+ * whatever the shape and mask sizes) and merge the partial (value, position) pairs with 64-bit
+ * atomics in `workspace`; when workspace is NULL or smaller than
  * snb_inf_dist_forward_workspace_bytes(B, CO) = 8 * B * CO bytes, it behaves exactly like
  * snb_inf_dist_forward.  The workspace needs 8-byte alignment, may hold anything on entry and holds
  * nothing of value on return; results are bit-identical to snb_inf_dist_forward.

@@ -35,7 +35,7 @@ struct InfFwdParams {
 
 constexpr int CHUNK_TILES = 1;  // argmax chunk = one k-tile = 32 reduction steps
 
-enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };  // inf_fwd_kernel is only instantiated for GATHER
+enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
 
 // Four reduction steps of one output: acc = max(acc, |x_k - w_k|), k = 0..3, operands given as
 // two 64-bit register pairs each.  All instruction forms of subtract + max cost two issue cycles
@@ -66,127 +66,6 @@ __device__ __forceinline__ void linf_step(float& acc, const ulonglong2& x, const
     unpack2(sub2(x.y, w.y), a, b);
     acc = max3abs(acc, a, b);
 #endif
-}
-
-template <int WM, int WN, int MODE, bool TRACK>
-__global__ void __launch_bounds__(WM* WN * 32) inf_fwd_kernel(const InfFwdParams p) {
-    constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
-    static_assert(MODE != MODE_GATHER || WM == 1, "masked tiles are one 32-row sub-batch");
-    extern __shared__ __align__(16) float smem[];
-    float* xs = smem;                 // [2][BM][LDS]
-    float* ws = smem + 2 * BM * LDS;  // [2][BN][LDS]
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wm = warp / WN, wn = warp % WN, tb = lane >> 3, tj = lane & 7;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-    const int nk = (p.CI + BK - 1) / BK;
-
-    GatherW<BN, NT> gw;
-    const int* ci_s = nullptr;
-    if (MODE == MODE_GATHER) {
-        const int s = m0 / SNB_SUB_BATCH;
-        ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
-        gw.init_rows(p.co ? p.co + (size_t)s * p.CO : nullptr, n0, p.CO, p.W_CI, tid);
-        gw.fetch_cols(ci_s, 0, p.CI, tid);
-    }
-
-    auto stage = [&](int kt, int st) {
-        float* xd = xs + st * BM * LDS;
-        float* wd = ws + st * BN * LDS;
-        if (MODE == MODE_VEC) {
-            stage_dense_vec<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
-            stage_dense_vec<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
-        } else if (MODE == MODE_SCALAR) {
-            stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
-            stage_dense_scalar<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
-        } else {
-            stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
-            gw.stage(wd, p.w, tid);
-        }
-    };
-
-    float acc[8][8];
-    float prev[TRACK ? 8 : 1][TRACK ? 8 : 1];
-    uint32_t q[TRACK ? 8 : 1][TRACK ? 4 : 1];  // two 16-bit chunk ids per word, 0xffff = none
-#pragma unroll
-    for (int i = 0; i < 8; i++)
-#pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = SNB_EPS;
-    if (TRACK) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) prev[i][j] = SNB_EPS;
-#pragma unroll
-            for (int j = 0; j < 4; j++) q[i][j] = 0xffffffffu;
-        }
-    }
-
-    stage(0, 0);
-    cp_async_commit();
-    if (MODE == MODE_GATHER && nk > 1) gw.fetch_cols(ci_s, BK, p.CI, tid);
-
-    for (int kt = 0; kt < nk; kt++) {
-        cp_async_wait<0>();
-        __syncthreads();
-        if (kt + 1 < nk) {
-            stage(kt + 1, (kt + 1) & 1);
-            // kept-column indices of the tile after next: their load latency hides behind this
-            // tile's arithmetic instead of stalling the next staging step
-            if (MODE == MODE_GATHER && kt + 2 < nk) gw.fetch_cols(ci_s, (kt + 2) * BK, p.CI, tid);
-        }
-        cp_async_commit();
-
-        const float* xr = xs + (kt & 1) * BM * LDS + (wm * 32 + tb) * LDS;
-        const float* wr = ws + (kt & 1) * BN * LDS + (wn * 64 + tj) * LDS;
-#pragma unroll 2
-        for (int kk = 0; kk < BK / 4; kk++) {
-            ulonglong2 xf[8], wf[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                xf[i] = *reinterpret_cast<const ulonglong2*>(xr + i * 4 * LDS + kk * 4);
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                wf[j] = *reinterpret_cast<const ulonglong2*>(wr + j * 8 * LDS + kk * 4);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    linf_step(acc[i][j], xf[i], wf[j]);
-                }
-            }
-        }
-        if (TRACK && (((kt % CHUNK_TILES) == CHUNK_TILES - 1) || kt == nk - 1)) {
-            const uint32_t chunk = (uint32_t)(kt / CHUNK_TILES);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    if (acc[i][j] > prev[i][j])
-                        q[i][j >> 1] = (j & 1) ? __byte_perm(q[i][j >> 1], chunk, 0x5410)
-                                               : __byte_perm(q[i][j >> 1], chunk, 0x3254);
-                    prev[i][j] = acc[i][j];
-                }
-            }
-        }
-    }
-
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int m = m0 + wm * 32 + tb + 4 * i;
-        if (m >= p.B) continue;
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const int n = n0 + wn * 64 + tj + 8 * j;
-            if (n >= p.CO) continue;
-            const size_t o = (size_t)m * p.CO + n;
-            p.y[o] = acc[i][j];
-            if (TRACK) {
-                uint32_t c = (j & 1) ? (q[i][j >> 1] >> 16) : (q[i][j >> 1] & 0xffffu);
-                p.pos[o] = c == 0xffffu ? -1 : (int)c;
-            }
-        }
-    }
 }
 
 // Turns the chunk id left in pos by the tracking kernel into the reference's argmax word.
@@ -308,16 +187,21 @@ __global__ void __launch_bounds__(256) inf_bwd_wide_kernel(const float* __restri
     }
 }
 
-// Dense forward without argmax words, stream-K over (tile, k-tile) pairs: every CTA of a
-// persistent grid does the same number of k-tiles, partial tiles are merged with atomicMax
-// (exact for max), so the run time does not depend on how the tile count divides the SMs.
+// Forward kernel (dense or index-masked operands, with or without argmax tracking), stream-K over
+// (tile, k-tile) pairs: every CTA of a persistent grid does the same number of k-tiles, so the
+// run time does not depend on how the tile count divides the SMs (with 32-row masked tiles and
+// Binomial mask sizes that count changes from step to step).  Partial tiles merge exactly:
+// plain values by atomicMax on the non-negative float patterns, (value, chunk) pairs by 64-bit
+// atomicMax on keys in caller-provided scratch; without scratch, tracking runs whole tiles only.
 struct InfSkParams {
     const float* x;
     const float* w;
     float* y;
     int* pos;                   // TRACK without workspace: receives chunk ids
     unsigned long long* keys;   // TRACK split over k: (value bits << 32 | 0xffffffff - chunk), zeroed
-    int B, CO, CI;
+    const int* ci;              // GATHER: kept columns / rows of W per 32-row sub-batch (or null)
+    const int* co;
+    int B, CO, CI, W_CI;
     int tiles_m, tiles_n;
 };
 
@@ -326,9 +210,10 @@ __device__ __forceinline__ unsigned long long pack_key(float v, uint32_t chunk16
     return ((unsigned long long)__float_as_uint(v) << 32) | lo;
 }
 
-template <int WM, int WN, bool VEC, bool TRACK>
+template <int WM, int WN, int MODE, bool TRACK>
 __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkParams p) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
+    static_assert(MODE != MODE_GATHER || WM == 1, "masked tiles are one 32-row sub-batch");
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;
     float* ws = smem + 2 * BM * LDS;
@@ -342,15 +227,26 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
         const int ka = (int)(u0 % sk.nk);
         const int kb = (int)min((long long)sk.nk, ka + (u1 - u0));
         const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+        GatherW<BN, NT> gw;
+        const int* ci_s = nullptr;
+        if (MODE == MODE_GATHER) {
+            const int s = m0 / SNB_SUB_BATCH;
+            ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
+            gw.init_rows(p.co ? p.co + (size_t)s * p.CO : nullptr, n0, p.CO, p.W_CI, tid);
+            gw.fetch_cols(ci_s, ka * BK, p.CI, tid);
+        }
         auto stage = [&](int kt, int st) {
             float* xd = xs + st * BM * LDS;
             float* wd = ws + st * BN * LDS;
-            if (VEC) {
+            if (MODE == MODE_VEC) {
                 stage_dense_vec<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
-                stage_dense_vec<BN, NT>(wd, p.w, n0, p.CO, p.CI, kt * BK, p.CI, tid);
+                stage_dense_vec<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
+            } else if (MODE == MODE_SCALAR) {
+                stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+                stage_dense_scalar<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
             } else {
                 stage_dense_scalar<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
-                stage_dense_scalar<BN, NT>(wd, p.w, n0, p.CO, p.CI, kt * BK, p.CI, tid);
+                gw.stage(wd, p.w, tid);
             }
         };
         float acc[8][8];
@@ -372,10 +268,16 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
         __syncthreads();  // the previous tile's readers are done with both stages
         stage(ka, ka & 1);
         cp_async_commit();
+        if (MODE == MODE_GATHER && ka + 1 < kb) gw.fetch_cols(ci_s, (ka + 1) * BK, p.CI, tid);
         for (int kt = ka; kt < kb; kt++) {
             cp_async_wait<0>();
             __syncthreads();
-            if (kt + 1 < kb) stage(kt + 1, (kt + 1) & 1);
+            if (kt + 1 < kb) {
+                stage(kt + 1, (kt + 1) & 1);
+                // kept-column indices of the tile after next: their load latency hides behind
+                // this tile's arithmetic
+                if (MODE == MODE_GATHER && kt + 2 < kb) gw.fetch_cols(ci_s, (kt + 2) * BK, p.CI, tid);
+            }
             cp_async_commit();
             const float* xr = xs + (kt & 1) * BM * LDS + (wm * 32 + tb) * LDS;
             const float* wr = ws + (kt & 1) * BN * LDS + (wn * 64 + tj) * LDS;
@@ -440,11 +342,11 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
 }
 
 // keys: 8 * B * CO bytes of scratch or null.  Without it a TRACK launch uses whole tiles only.
-template <int WM, int WN, bool VEC, bool TRACK>
+template <int WM, int WN, int MODE, bool TRACK>
 static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
     constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
-    auto kern = inf_fwd_sk_kernel<WM, WN, VEC, TRACK>;
+    auto kern = inf_fwd_sk_kernel<WM, WN, MODE, TRACK>;
     static int ctas_per_sm[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -478,68 +380,19 @@ static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
 // *split tells whether tiles were shared between CTAs; for TRACK that means the result is in
 // `keys` (workspace) and still has to be turned into y / pos by the resolve kernel.
 template <bool TRACK>
-static cudaError_t dispatch_sk(const InfFwdParams& q, unsigned long long* keys, bool* split, cudaStream_t st) {
-    InfSkParams p{q.x, q.w, q.y, q.pos, keys, q.B, q.CO, q.CI, 0, 0};
-    const bool vec = (q.CI % 4 == 0) && aligned16(q.x) && aligned16(q.w);
+static cudaError_t dispatch_fwd(const InfFwdParams& q, unsigned long long* keys, bool* split, cudaStream_t st) {
+    InfSkParams p{q.x, q.w, q.y, q.pos, keys, q.ci, q.co, q.B, q.CO, q.CI, q.W_CI, 0, 0};
+    const int sms = sm_count();
+    if (q.ci || q.co) {
+        const long wide = (long)((q.B + 31) / 32) * ((q.CO + 255) / 256);
+        return wide >= sms / 2 ? launch_sk<1, 4, MODE_GATHER, TRACK>(p, split, st)
+                               : launch_sk<1, 2, MODE_GATHER, TRACK>(p, split, st);
+    }
+    const bool vec = (q.CI % 4 == 0) && (q.W_CI % 4 == 0) && aligned16(q.x) && aligned16(q.w);
     const long big = (long)((q.B + 63) / 64) * ((q.CO + 127) / 128);
-    if (big >= sm_count())
-        return vec ? launch_sk<2, 2, true, TRACK>(p, split, st) : launch_sk<2, 2, false, TRACK>(p, split, st);
-    return vec ? launch_sk<1, 2, true, TRACK>(p, split, st) : launch_sk<1, 2, false, TRACK>(p, split, st);
-}
-
-template <int WM, int WN, int MODE, bool TRACK>
-struct FwdLaunch {
-    static constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
-    static constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
-    // Resident CTAs per SM of this instantiation on the current device (cached); 0 on error.
-    static int ctas_per_sm(cudaError_t* err) {
-        static int cached[64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        int& cps = cached[dev & 63];
-        if (cps == 0) {
-            auto kern = inf_fwd_kernel<WM, WN, MODE, TRACK>;
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-            int occ = 0;
-            if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
-            if (e != cudaSuccess) {
-                *err = e;
-                return 0;
-            }
-            cps = occ > 0 ? occ : 1;
-        }
-        return cps;
-    }
-    // Relative run time: waves x (work per wave per SM).
-    static double cost(const InfFwdParams& p, cudaError_t* err) {
-        const int cps = ctas_per_sm(err);
-        if (cps == 0) return 1e300;
-        const long long tiles = (long long)((p.B + BM - 1) / BM) * ((p.CO + BN - 1) / BN);
-        const long long slots = (long long)sm_count() * cps;
-        const long long waves = (tiles + slots - 1) / slots;
-        return (double)waves * cps * BM * BN;
-    }
-    static cudaError_t launch(const InfFwdParams& p, cudaStream_t st) {
-        cudaError_t err = cudaSuccess;
-        if (ctas_per_sm(&err) == 0) return err;
-        dim3 grid((p.B + BM - 1) / BM, (p.CO + BN - 1) / BN);
-        inf_fwd_kernel<WM, WN, MODE, TRACK><<<grid, NT, SMEM, st>>>(p);
-        return cudaGetLastError();
-    }
-};
-
-template <bool TRACK>
-static cudaError_t dispatch_fwd(const InfFwdParams& p, unsigned long long* keys, bool* split, cudaStream_t st) {
-    *split = false;
-    if (p.ci || p.co) {
-        cudaError_t err = cudaSuccess;
-        const double c4 = FwdLaunch<1, 4, MODE_GATHER, TRACK>::cost(p, &err);
-        const double c2 = FwdLaunch<1, 2, MODE_GATHER, TRACK>::cost(p, &err);
-        if (err != cudaSuccess) return err;
-        return c4 <= c2 ? FwdLaunch<1, 4, MODE_GATHER, TRACK>::launch(p, st)
-                        : FwdLaunch<1, 2, MODE_GATHER, TRACK>::launch(p, st);
-    }
-    return dispatch_sk<TRACK>(p, keys, split, st);
+    if (big >= sms)
+        return vec ? launch_sk<2, 2, MODE_VEC, TRACK>(p, split, st) : launch_sk<2, 2, MODE_SCALAR, TRACK>(p, split, st);
+    return vec ? launch_sk<1, 2, MODE_VEC, TRACK>(p, split, st) : launch_sk<1, 2, MODE_SCALAR, TRACK>(p, split, st);
 }
 
 cudaError_t inf_forward_values(const float* x, const float* w, float* y, const int* ci, const int* co,

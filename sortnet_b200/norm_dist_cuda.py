@@ -120,16 +120,12 @@ def inf_dist_forward(input, weight, output, pos, G, w_index_ci=None, w_index_co=
     if output.size(0) != B or pos.shape != output.shape:
         raise RuntimeError("output / pos shape mismatch")
     dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
-    if w_index_ci is None and w_index_co is None:
-        # scratch for the k-split merge of (value, position) pairs: 8 bytes per output
-        ws = torch.empty(B * CO, dtype=torch.int64, device=dev)
-        _call(dev, input, "snb_inf_dist_forward_ws", (B, CO, CI),
-              _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos), None, None,
-              weight.size(0), weight.size(1) * G, ws.data_ptr(), ws.numel() * 8)
-        return
-    _call(dev, input, "snb_inf_dist_forward", (B, CO, CI),
+    # scratch for the k-split merge of (value, position) pairs: 8 bytes per output, taken from
+    # PyTorch's caching allocator (stream-ordered, no device synchronisation)
+    ws = torch.empty(B * CO, dtype=torch.int64, device=dev)
+    _call(dev, input, "snb_inf_dist_forward_ws", (B, CO, CI),
           _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos), _ptr(w_index_ci),
-          _ptr(w_index_co), weight.size(0), weight.size(1) * G)
+          _ptr(w_index_co), weight.size(0), weight.size(1) * G, ws.data_ptr(), ws.numel() * 8)
 
 
 def inf_dist_forward_nograd(input, weight, output, G):

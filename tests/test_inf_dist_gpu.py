@@ -123,6 +123,33 @@ def test_workspace_and_plain_entry_points_agree(B, CI, CO):
         assert np.array_equal(host(y), y_o) and np.array_equal(host(pos), pos_o)
 
 
+@pytest.mark.parametrize("B,CI,CO,keep", [(512, 1024, 2100, 0.9), (96, 300, 520, 0.8), (500, 640, 5000, 0.9)])
+def test_masked_workspace_and_plain_entry_points_agree(B, CI, CO, keep):
+    from sortnet_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(CO + 1)
+    ci, co = make_masks(rng, B, CI, keep), make_masks(rng, B, CO, keep)
+    x = (rng.integers(0, 8, (B, ci.shape[1])) / 8).astype(np.float32)
+    w = (rng.integers(-16, 17, (CO, CI)) / 8).astype(np.float32)
+    y_o, pos_o = oracle.inf_dist_forward(x, w, ci, co)
+    X, W, CIt, COt = col3(x), dev(w), idx3(ci), idx3(co)
+    st = torch.cuda.current_stream().cuda_stream
+    n_in, n_out = ci.shape[1], co.shape[1]
+    for use_ws in (False, True):
+        y = torch.zeros(B, n_out, 1, device="cuda")
+        pos = torch.zeros(B, n_out, 1, device="cuda", dtype=torch.int32)
+        if use_ws:
+            ws = torch.full((B * n_out,), -1, dtype=torch.int64, device="cuda")
+            rc = lib.snb_inf_dist_forward_ws(X.data_ptr(), W.data_ptr(), B, n_out, n_in, 1, 1, y.data_ptr(),
+                                             pos.data_ptr(), CIt.data_ptr(), COt.data_ptr(), CO, CI,
+                                             ws.data_ptr(), ws.numel() * 8, st)
+        else:
+            rc = lib.snb_inf_dist_forward(X.data_ptr(), W.data_ptr(), B, n_out, n_in, 1, 1, y.data_ptr(),
+                                          pos.data_ptr(), CIt.data_ptr(), COt.data_ptr(), CO, CI, st)
+        assert rc == 0
+        assert np.array_equal(host(y), y_o) and np.array_equal(host(pos), pos_o)
+
+
 def test_ties_floor_and_sign():
     # quantised inputs force many exact ties: lowest index must win, sign from x - w
     rng = np.random.default_rng(7)
