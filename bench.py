@@ -37,11 +37,11 @@ WORKLOAD = {
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (bound_fwd_kernel_512x5120x5120.md, inf_fwd_kernel_masked_512x4619x4596.md), at the
-# shapes of the widest layers of this workload.
+# profiles/ (bound_fwd_tma_kernel_512x5120x5120.md; inf_fwd_sk_kernel_masked_512x4619x4596.md,
+# forward + resolve kernels), at the shapes of the widest layers of this workload.
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "snb_bound_inf_dist_forward_nograd": 201.8e6,
-    "snb_inf_dist_forward_ws": 120.4e6,
+    "snb_bound_inf_dist_forward_nograd": 202.7e6,
+    "snb_inf_dist_forward_ws": 262.2e6,
 }
 
 

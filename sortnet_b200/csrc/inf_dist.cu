@@ -71,10 +71,12 @@ __device__ __forceinline__ void linf_step(float& acc, const ulonglong2& x, const
 // Turns the chunk id left in pos by the tracking kernel into the reference's argmax word.
 // One warp owns 32 consecutive outputs of one row; for each of them the 32 lanes load the 32
 // elements of its chunk (coalesced in x, one row segment of W), compare with y and the lowest
-// matching lane gives the index.  Four outputs are in flight per warp to overlap the
-// index -> weight load chains.
+// matching lane gives the index.  RESOLVE_BATCH outputs are in flight per warp to overlap the
+// index -> weight load chains (the kernel is bound by their latency).
 // FROM_WS: the tracking kernel ran split over k and left (value bits << 32 | ~chunk) keys in the
 // 64-bit workspace instead of y / pos; y is written here too.
+constexpr int RESOLVE_BATCH = 8;
+
 template <bool FROM_WS>
 __global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, const unsigned long long* __restrict__ keys) {
     static_assert(CHUNK_TILES * BK == 32, "one lane per chunk element");
@@ -104,12 +106,12 @@ __global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, 
     const int* ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
     uint32_t my_word = 0;
 #pragma unroll 1
-    for (int base = 0; base < 32; base += 4) {
-        int col[4];
-        float xv[4], yv[4], wv[4];
-        int rowv[4];
+    for (int base = 0; base < 32; base += RESOLVE_BATCH) {
+        int col[RESOLVE_BATCH];
+        float xv[RESOLVE_BATCH], yv[RESOLVE_BATCH], wv[RESOLVE_BATCH];
+        int rowv[RESOLVE_BATCH];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < RESOLVE_BATCH; u++) {
             const int chunk = __shfl_sync(0xffffffffu, my_chunk, base + u);
             yv[u] = __shfl_sync(0xffffffffu, my_y, base + u);
             rowv[u] = __shfl_sync(0xffffffffu, my_row, base + u);
@@ -119,9 +121,9 @@ __global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, 
             xv[u] = ok ? xr[c] : 0.f;
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) wv[u] = col[u] >= 0 ? p.w[(size_t)rowv[u] * p.W_CI + col[u]] : 0.f;
+        for (int u = 0; u < RESOLVE_BATCH; u++) wv[u] = col[u] >= 0 ? p.w[(size_t)rowv[u] * p.W_CI + col[u]] : 0.f;
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < RESOLVE_BATCH; u++) {
             const float t = xv[u] - wv[u];
             const uint32_t hits = __ballot_sync(0xffffffffu, col[u] >= 0 && fabsf(t) == yv[u]);
             const int first = hits ? __ffs(hits) - 1 : 0;
