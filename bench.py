@@ -232,9 +232,10 @@ def run_gpu_arm(args):
                 work.wait()
             opt.step()
         else:
-            # Measured at N = 8: hiding the exchange behind the bound kernels costs more than it
+            # Measured at N = 8: hiding an NCCL exchange behind the bound kernels costs more than it
             # saves (NCCL's CTAs hold SMs that the one-wave compute kernels are sized for:
-            # 27.8 ms per step overlapped, 26.0 ms exposed), so the default is one exposed all-reduce.
+            # 27.8 ms per step overlapped, 26.0 ms exposed), so the exchange is not overlapped: it
+            # is part of step() (peer-memory kernel) or one flat all-reduce right before it.
             opt.all_reduce()
             opt.step()
             with torch.no_grad():

@@ -273,3 +273,34 @@ class SortMLPModel(nn.Module):
         margin = score_hi - torch.gather(score_lo, 1, targets.view(-1, 1))
         margin = margin.scatter(1, targets.view(-1, 1), 0)
         return score * self.scalar, margin / (2 * eps)
+
+
+@torch.no_grad()
+def update_running_means(model, batches, process_group=None):
+    """Re-estimates every mean-shift layer's running mean before certification, as the
+    reference's `update_bn` does (main.py:184-202): one pass over `batches` (an iterable of input
+    tensors) in training mode at p = inf with momentum 1 / (k + 1) for the k-th batch, i.e. a
+    plain average of the batch means, then the mean over ranks.  Layer p values, momenta and the
+    training flag are restored."""
+    from .dist import all_reduce_mean_
+    shifts = [m for m in model.modules() if isinstance(m, MeanShiftDropout)]
+    layers = [m for m in model.modules() if isinstance(m, NormDist)]
+    saved_p = [l.p for l in layers]
+    saved_momentum = [m.momentum for m in shifts]
+    was_training = model.training
+    model.train()
+    for l in layers:
+        l.p = float("inf")
+    try:
+        for k, x in enumerate(batches):
+            for m in shifts:
+                m.momentum = 1.0 / (k + 1)
+            model(x)
+        for m in shifts:
+            all_reduce_mean_(m.running_mean, process_group)
+    finally:
+        for m, mom in zip(shifts, saved_momentum):
+            m.momentum = mom
+        for l, p_val in zip(layers, saved_p):
+            l.p = p_val
+        model.train(was_training)

@@ -81,3 +81,21 @@ def test_reference_operator_layer_runs_on_these_kernels():
     assert torch.equal(y, y2)
     with pytest.raises(RuntimeError):
         ops.norm_dist(x, w, 2.0, use_custom_cuda_func=False)
+
+
+def test_update_running_means_is_the_average_of_batch_means():
+    from sortnet_b200.layers import SortMLPModel, update_running_means
+    torch.manual_seed(3)
+    model = SortMLPModel(depth=3, width=64, input_dim=(1, 4, 4), num_classes=5, dropout=1.0).cuda()
+    model.set_p(8.0)
+    batches = [torch.rand(64, 1, 4, 4, device="cuda") for _ in range(3)]
+    update_running_means(model, batches)
+    assert all(l.p == 8.0 for l in model.fc_dist) and model.training
+    assert model.fc_dist[0].mean_shift.momentum == 0.1
+    # first layer: its input does not depend on any running mean, so the expected value is direct
+    from sortnet_b200 import ops
+    w = model.fc_dist[0].weight
+    means = [ops.norm_dist(b.reshape(64, -1, 1), w, float("inf")).mean(dim=(0, 2)) for b in batches]
+    want = torch.stack(means).mean(dim=0)
+    got = model.fc_dist[0].mean_shift.running_mean
+    assert (got - want).abs().max() <= 1e-5 * want.abs().max()
