@@ -124,15 +124,16 @@ __global__ void __launch_bounds__(256) sort_fwd_kernel(const SortParams p) {
                         const float t1 = wv[j] - xv[i], t2 = uv[i] - wv[j];
                         const float vl = fminf(t1, t2), vu = fmaxf(t1, t2);
                         // A value that does not beat the weakest slot leaves the whole list
-                        // unchanged, so the chain is only walked when some lane needs it (after the
-                        // first few hundred columns that is a minority of the steps).
-                        if (vl < rl[i][j][0]) {
+                        // unchanged, so the chain is only walked when some lane of the warp needs it
+                        // (a warp vote keeps the branch uniform; after the first few hundred columns
+                        // that is a minority of the steps).
+                        if (__any_sync(0xffffffffu, vl < rl[i][j][0])) {
 #pragma unroll
                             for (int s = 0; s < KMAX - 1; s++)
                                 rl[i][j][s] = fminf(rl[i][j][s], fmaxf(rl[i][j][s + 1], vl));
                             rl[i][j][KMAX - 1] = fminf(rl[i][j][KMAX - 1], vl);
                         }
-                        if (vu > ru[i][j][0]) {
+                        if (__any_sync(0xffffffffu, vu > ru[i][j][0])) {
 #pragma unroll
                             for (int s = 0; s < KMAX - 1; s++)
                                 ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], vu));
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(256) sort_fwd_kernel(const SortParams p) {
                         }
                     } else {
                         const float v = fabsf(xv[i] - wv[j]);
-                        if (v > ru[i][j][0]) {
+                        if (__any_sync(0xffffffffu, v > ru[i][j][0])) {
 #pragma unroll
                             for (int s = 0; s < KMAX - 1; s++)
                                 ru[i][j][s] = fmaxf(ru[i][j][s], fminf(ru[i][j][s + 1], v));
