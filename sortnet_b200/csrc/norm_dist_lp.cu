@@ -270,6 +270,7 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
             gx[i][k] = 0.f;
         }
 
+    const int mycol = tb == 0 ? col[0] : tb == 1 ? col[1] : tb == 2 ? col[2] : col[3];
     const int ntiles = (p.CO + LPB_JT - 1) / LPB_JT;
     // |u|^(p-1) < 2^-40 for a whole warp: the terms are dropped (the largest terms are ~1)
     const bool use_skip = p.pm1 >= 48.0f;
@@ -313,9 +314,13 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
 #pragma unroll
         for (int r = 0; r < 1024 / NT; r++) {  // y -> 1/y (0 for padding), each thread its own elements
             const int e = tid + NT * r;
-            float* q = yt + (st * LPB_JT + (e & 31)) * 33 + (e >> 5);
-            const float v = *q;
-            *q = v > 0.f ? 1.0f / v : 0.f;
+            const int o = (st * LPB_JT + (e & 31)) * 33 + (e >> 5);
+            const float v = yt[o];
+            const float ry = v > 0.f ? 1.0f / v : 0.f;
+            yt[o] = ry;
+            // integer exponents: g * (|t| / y)^IP = (g / y^IP) * |t|^IP, so the division by y is
+            // folded into g once per (row, output) instead of once per term
+            if (IP >= 0) gt[o] *= pow_abs<IP>(ry, 0.f);
         }
         __syncthreads();
         const int j0 = t * LPB_JT;
@@ -329,13 +334,12 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
             if (IP >= 0) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
-                    const float gv = gp[i], ry = yp[i];
+                    const float gv = gp[i];   // already divided by y^IP
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
-                        const float u = (xv[i][k] - wv[k]) * ry;
-                        const float term = gv * pow_signed<IP>(u, p.pm1);
-                        gx[i][k] += term;
-                        gwp[k] += term;
+                        const float ps = pow_signed<IP>(xv[i][k] - wv[k], p.pm1);
+                        gx[i][k] = fmaf(gv, ps, gx[i][k]);
+                        gwp[k] = fmaf(gv, ps, gwp[k]);
                     }
                 }
             } else {
@@ -385,11 +389,13 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
                     gwp[k] += __shfl_xor_sync(0xffffffffu, gwp[k], 1);
                     gwp[k] += __shfl_xor_sync(0xffffffffu, gwp[k], 2);
                 }
-                if (tb == 0) {
+                // after the butterfly every lane holds all four column sums; lane tb sends column
+                // tb, so the warp issues ONE reduction instruction per output row covering 32
+                // neighbouring kept columns (4-5 sectors) instead of four instructions from 8 lanes
+                {
                     const int row = co_s ? co_s[j0 + jj] : j0 + jj;
-#pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        if (col[k] >= 0) atomicAdd(p.gw + (size_t)row * p.W_CI + col[k], -gwp[k]);
+                    const float v = tb == 0 ? gwp[0] : tb == 1 ? gwp[1] : tb == 2 ? gwp[2] : gwp[3];
+                    if (mycol >= 0) atomicAdd(p.gw + (size_t)row * p.W_CI + mycol, -v);
                 }
             }
         }
