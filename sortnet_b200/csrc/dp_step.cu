@@ -12,7 +12,7 @@
 // rank, so all replicas stay bit-identical.  Ordering between ranks (gradients complete before
 // they are read, parameters complete before the next forward reads them) is provided by the
 // caller with stream-ordered barriers around the launch; the kernel itself never waits.
-// No multicast loads, no multimem: ordinary ld / st on peer pointers.
+// Only ordinary ld / st instructions touch peer pointers.
 #include "common.cuh"
 #include "launch.h"
 

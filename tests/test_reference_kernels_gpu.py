@@ -155,3 +155,70 @@ def test_sort_neuron(ref, B, CI, CO, q, K):
     torch.cuda.synchronize()
     assert (gx_r - gx_m).abs().max() <= 1e-5 * gx_r.abs().max()
     assert (gw_r - gw_m).abs().max() <= 1e-5 * gw_r.abs().max()
+
+
+def _time(fn, n=3, warm=1):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / n
+
+
+def test_timings_against_the_reference_kernels(ref, capsys):
+    """GPU comparator: the reference's kernels and these on the widest layer of the benchmark
+    workload (B = 512, 5120 x 5120 weights, keep 0.9).  Prints a table (run with -s) and only
+    gates that nothing here is slower than the reference's kernel."""
+    from sortnet_b200 import norm_dist_cuda as C
+    from sortnet_b200.layers import sample_mask
+    dev = "cuda"
+    B, CIF, COF = 512, 5120, 5120
+    torch.manual_seed(0)
+    ci, co = sample_mask(16, 1, CIF, 0.9, dev), sample_mask(16, 1, COF, 0.9, dev)
+    CI, CO = ci.size(-1), co.size(-1)
+    w = torch.randn(COF, CIF, device=dev)
+    x = torch.rand(B, CI, 1, device=dev)
+    y = torch.empty(B, CO, 1, device=dev)
+    pos = torch.empty(B, CO, 1, device=dev, dtype=torch.int32)
+    g = torch.randn(B, CO, 1, device=dev)
+    gx, gw = torch.empty_like(x), torch.empty_like(w)
+    xd = torch.rand(B, CIF, 1, device=dev)
+    yd, yd2 = torch.empty(B, COF, 1, device=dev), torch.empty(B, COF, 1, device=dev)
+    xl, xu = (xd - 0.03).clamp(0, 1), (xd + 0.03).clamp(0, 1)
+    ref.inf_dist_forward(x, w, y, pos, 1, ci, co)
+    cases = [
+        ("inf_dist_forward, masked", lambda: ref.inf_dist_forward(x, w, y, pos, 1, ci, co),
+         lambda: C.inf_dist_forward(x, w, y, pos, 1, ci, co)),
+        ("inf_dist_backward_input_weight, masked", lambda: ref.inf_dist_backward_input_weight(g, pos, gx, gw, 1, ci, co),
+         lambda: C.inf_dist_backward_input_weight(g, pos, gx, gw, 1, ci, co)),
+        ("inf_dist_forward_nograd", lambda: ref.inf_dist_forward_nograd(xd, w, yd, 1),
+         lambda: C.inf_dist_forward_nograd(xd, w, yd, 1)),
+        ("bound_inf_dist_forward_nograd", lambda: ref.bound_inf_dist_forward_nograd(xl, xu, w, yd, yd2, 1),
+         lambda: C.bound_inf_dist_forward_nograd(xl, xu, w, yd, yd2, 1)),
+    ]
+    for p in (8.0, 31.6):
+        cases.append(("norm_dist_forward, masked, p=%g" % p, lambda p=p: ref.norm_dist_forward(x, w, y, 1, p, ci, co),
+                      lambda p=p: C.norm_dist_forward(x, w, y, 1, p, ci, co)))
+        cases.append(("norm_dist_backward_input_weight, masked, p=%g" % p,
+                      lambda p=p: ref.norm_dist_backward_input_weight(g, x, w, y, gx, gw, 1, p, ci, co),
+                      lambda p=p: C.norm_dist_backward_input_weight(g, x, w, y, gx, gw, 1, p, ci, co)))
+    cases.append(("sort_neuron_forward_nograd, q=0.9, K=10", lambda: ref.sort_neuron_forward_nograd(xd, w, yd, 1, 0.9, 10),
+                  lambda: C.sort_neuron_forward_nograd(xd, w, yd, 1, 0.9, 10)))
+    cases.append(("bound_sort_neuron_forward, q=0.9, K=10",
+                  lambda: ref.bound_sort_neuron_forward(xl, xu, w, yd, yd2, 1, 0.9, 10),
+                  lambda: C.bound_sort_neuron_forward(xl, xu, w, yd, yd2, 1, 0.9, 10)))
+    rows = []
+    for name, f_ref, f_mine in cases:
+        t_ref, t_mine = _time(f_ref), _time(f_mine)
+        rows.append((name, t_ref, t_mine))
+    with capsys.disabled():
+        print()
+        for name, t_ref, t_mine in rows:
+            print("%-48s reference %8.3f ms   this library %8.3f ms   x%.2f" % (name, t_ref, t_mine, t_ref / t_mine))
+    for name, t_ref, t_mine in rows:
+        assert t_mine <= 1.25 * t_ref, name
