@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the reference's own Python code.
 
-Run once, in a container that has the reference checkout (path in $SORTNET_REFERENCE,
-default /root/reference):   python tests/golden/make_golden.py
+Run once, in a container that has the reference checkout (path in $SORTNET_REFERENCE, default
+the REF constant below):   python tests/golden/make_golden.py
 
 The reference's pure-PyTorch branches are imported unmodified with a CPU stand-in for
 its CUDA extension module, evaluated on CPU on small seeded inputs, and their outputs and

@@ -1,4 +1,4 @@
-"""The layer shapes of the five BASELINE configurations at full size.
+"""The layer shapes of the five benchmark configurations of this project at full size.
 
 The oracle is run on a sample of batch rows (whole sub-batches, so the masks apply unchanged) and
 compared bit for bit; every output is additionally checked through size-independent properties:
