@@ -203,7 +203,26 @@ def run_gpu_arm(args):
     # N > 1: gradient exchange and optimiser are one kernel over NVLink peer memory
     # (SNB_PEER_STEP=0 falls back to one NCCL all-reduce followed by the local fused AdamW)
     peer_step = world > 1 and os.environ.get("SNB_PEER_STEP", "1") != "0"
-    opt = FlatAdamW(model, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, peer_memory=peer_step)
+    adam = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
+    exchange = "none (single GPU)"
+    if peer_step:
+        try:
+            opt = FlatAdamW(model, peer_memory=True, **adam)
+            exchange = "fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory"
+        except Exception as exc:                          # symmetric memory not available: use NCCL
+            if rank == 0:
+                print("peer-memory step unavailable (%s); using one NCCL all-reduce" % exc, file=sys.stderr)
+            peer_step = False
+    if not peer_step:
+        opt = FlatAdamW(model, peer_memory=False, **adam)
+        if world > 1:
+            exchange = "one flat NCCL all-reduce + local fused AdamW"
+    # every rank must have taken the same path
+    if world > 1:
+        flag = torch.tensor([1.0 if peer_step else 0.0], device=dev)
+        dist.all_reduce(flag)
+        if 0.0 < float(flag) < world:
+            raise SystemExit("ranks disagree on the gradient-exchange path")
 
     pool = 4
     gen = torch.Generator().manual_seed(100 + rank)
@@ -384,6 +403,7 @@ def run_gpu_arm(args):
             "e2e": {"value": round(e2e, 1), "unit": "samples/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
             "gpu_launches": launches,
+            "gradient_exchange": exchange,
             "clocks": clocks,
             "roofline": dominant,
             "roofline_linf_forward": roofs.get("snb_inf_dist_forward_ws"),
