@@ -195,6 +195,92 @@ def case_model(seed, B, depth, width, input_dim, classes, q, p, eps):
     return out
 
 
+# ---- grouped / spatial shapes: x [B, G*CIg, HW], w [G*COg, CIg] ------------------------------
+
+def gen_g(seed, B, G, CIg, COg, HW):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.rand(B, G * CIg, HW, generator=g)
+    w = torch.randn(G * COg, CIg, generator=g)
+    gy = torch.randn(B, G * COg, HW, generator=g)
+    return x, w, gy
+
+
+def no_ties_inf_g(x, w, G):
+    B, C, HW = x.shape
+    d = (x.view(B, G, 1, -1, HW) - w.view(G, -1, w.size(-1), 1)).abs()
+    top2 = d.topk(2, dim=3)[0]
+    return bool((top2[:, :, :, 0] > top2[:, :, :, 1]).all())
+
+
+def case_norm_dist_g(seed, B, G, CIg, COg, HW, p):
+    x, w, gy = gen_g(seed, B, G, CIg, COg, HW)
+    if p == INF:
+        assert no_ties_inf_g(x, w, G), "pick another seed: tie in the max"
+    xp = x.clone().requires_grad_()
+    wp = w.clone().requires_grad_()
+    y = ref_ops.norm_dist(xp, wp, p, groups=G, use_custom_cuda_func=False)
+    y.backward(gy)
+    return dict(x=x, w=w, gy=gy, p=np.float64(p), G=np.int64(G), y=y.detach(), gx=xp.grad, gw=wp.grad)
+
+
+def case_dropout_g(seed, B, G, CIg_full, COg_full, HW, q, p):
+    torch.manual_seed(seed)
+    S = (B - 1) // 32 + 1
+    ci = sample_mask(S, G, CIg_full, q, device="cpu")
+    co = sample_mask(S, G, COg_full, q, device="cpu")
+    g = torch.Generator().manual_seed(seed + 1000)
+    x = torch.rand(B, G * ci.size(-1), HW, generator=g)
+    w = torch.randn(G * COg_full, CIg_full, generator=g)
+    gy = torch.randn(B, G * co.size(-1), HW, generator=g)
+    xp = x.clone().requires_grad_()
+    wp = w.clone().requires_grad_()
+    saved = ref_ops.norm_dist
+    ref_ops.norm_dist = functools.partial(saved, use_custom_cuda_func=False)
+    try:
+        y = ref_ops.norm_dist_dropout(xp, wp, ci, co, p, groups=G, use_custom_cuda_func=False)
+    finally:
+        ref_ops.norm_dist = saved
+    y.backward(gy)
+    if p == INF:
+        w3 = w.view(G, COg_full, CIg_full)
+        for s in range(S):
+            ws = torch.stack([w3[k][co[s, k].long()][:, ci[s, k].long()] for k in range(G)])
+            assert no_ties_inf_g(x[s * 32:(s + 1) * 32], ws.view(-1, ws.size(-1)), G), "pick another seed"
+    return dict(x=x, w=w, gy=gy, p=np.float64(p), G=np.int64(G), ci=ci, co=co, y=y.detach(),
+                gx=xp.grad, gw=wp.grad)
+
+
+def case_bound_g(seed, B, G, CIg, COg, HW, eps):
+    x, w, gl = gen_g(seed, B, G, CIg, COg, HW)
+    gu = torch.randn(gl.shape, generator=torch.Generator().manual_seed(seed + 7))
+    xl = (x - eps).clamp(0, 1)
+    xu = (x + eps).clamp(0, 1)
+    lp = xl.clone().requires_grad_()
+    up = xu.clone().requires_grad_()
+    wp = w.clone().requires_grad_()
+    yl, yu = ref_ops.bound_inf_dist(lp, up, wp, groups=G, use_custom_cuda_func=False)
+    w4 = w.view(G, -1, w.size(-1), 1)
+    x1 = w4 - xl.view(B, G, 1, -1, HW)
+    x2 = xu.view(B, G, 1, -1, HW) - w4
+    hi = torch.maximum(x1, x2).topk(2, dim=3)[0]
+    lo = (-torch.minimum(x1, x2)).topk(2, dim=3)[0]
+    assert bool((hi[:, :, :, 0] > hi[:, :, :, 1]).all()) and bool((lo[:, :, :, 0] > lo[:, :, :, 1]).all())
+    assert bool((x1 != x2).all())
+    (yl * gl).sum().add((yu * gu).sum()).backward()
+    return dict(xl=xl, xu=xu, w=w, gl=gl, gu=gu, G=np.int64(G), yl=yl.detach(), yu=yu.detach(),
+                gxl=lp.grad, gxu=up.grad, gw=wp.grad)
+
+
+def case_sort_g(seed, B, G, CIg, COg, HW, q, K):
+    x, w, gy = gen_g(seed, B, G, CIg, COg, HW)
+    xp = x.clone().requires_grad_()
+    wp = w.clone().requires_grad_()
+    y = ref_ops.sort_neuron(xp, wp, groups=G, q=q, truncate=K, use_custom_cuda_func=False)
+    y.backward(gy)
+    return dict(x=x, w=w, gy=gy, q=np.float64(q), K=np.int64(K), G=np.int64(G), y=y.detach(),
+                gx=xp.grad, gw=wp.grad)
+
+
 def save(name, d):
     arrs = {k: (v.detach().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in d.items()}
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrs)
@@ -202,25 +288,39 @@ def save(name, d):
 
 
 def main():
+    """With arguments, only the fixtures whose name starts with one of them are (re)written."""
     torch.set_num_threads(8)
-    save("norm_dist_inf_a", case_norm_dist(0, 70, 48, 40, INF))
-    save("norm_dist_inf_b", case_norm_dist(1, 33, 17, 5, INF))
-    save("norm_dist_p2", case_norm_dist(2, 37, 29, 21, 2.0))
-    save("norm_dist_p8", case_norm_dist(3, 70, 48, 40, 8.0))
-    save("norm_dist_p31", case_norm_dist(4, 40, 50, 24, 31.6))
-    save("norm_dist_p3", case_norm_dist(5, 19, 23, 11, 3.0))
-    save("dropout_inf", case_dropout(10, 70, 48, 40, 0.8, INF))
-    save("dropout_p8", case_dropout(11, 70, 48, 40, 0.8, 8.0))
-    save("dropout_p20", case_dropout(12, 45, 30, 36, 0.7, 20.0))
-    save("bound_a", case_bound(20, 70, 48, 40, 0.3))
-    save("bound_b", case_bound(21, 33, 17, 5, 0.03))
-    save("sort_a", case_sort(30, 20, 48, 12, 0.6, 10))
-    save("mean_shift_masked", case_mean_shift(40, 70, 40, 0.8))
-    save("mean_shift_plain", case_mean_shift(41, 45, 24, None))
-    save("model_inf_masked", case_model(50, 70, 4, 96, (3, 4, 4), 10, 0.8, INF, 0.03))
-    save("model_p8_masked", case_model(51, 70, 4, 96, (3, 4, 4), 10, 0.8, 8.0, 0.03))
-    save("model_inf_plain", case_model(52, 45, 3, 64, (3, 4, 4), 10, 1.0, INF, 0.03))
-
+    want = sys.argv[1:]
+    cases = [
+        ("norm_dist_inf_a", case_norm_dist, (0, 70, 48, 40, INF,)),
+        ("norm_dist_inf_b", case_norm_dist, (1, 33, 17, 5, INF,)),
+        ("norm_dist_p2", case_norm_dist, (2, 37, 29, 21, 2.0,)),
+        ("norm_dist_p8", case_norm_dist, (3, 70, 48, 40, 8.0,)),
+        ("norm_dist_p31", case_norm_dist, (4, 40, 50, 24, 31.6,)),
+        ("norm_dist_p3", case_norm_dist, (5, 19, 23, 11, 3.0,)),
+        ("dropout_inf", case_dropout, (10, 70, 48, 40, 0.8, INF,)),
+        ("dropout_p8", case_dropout, (11, 70, 48, 40, 0.8, 8.0,)),
+        ("dropout_p20", case_dropout, (12, 45, 30, 36, 0.7, 20.0,)),
+        ("bound_a", case_bound, (20, 70, 48, 40, 0.3,)),
+        ("bound_b", case_bound, (21, 33, 17, 5, 0.03,)),
+        ("sort_a", case_sort, (30, 20, 48, 12, 0.6, 10,)),
+        ("mean_shift_masked", case_mean_shift, (40, 70, 40, 0.8,)),
+        ("mean_shift_plain", case_mean_shift, (41, 45, 24, None,)),
+        ("model_inf_masked", case_model, (50, 70, 4, 96, (3, 4, 4), 10, 0.8, INF, 0.03,)),
+        ("model_p8_masked", case_model, (51, 70, 4, 96, (3, 4, 4), 10, 0.8, 8.0, 0.03,)),
+        ("model_inf_plain", case_model, (52, 45, 3, 64, (3, 4, 4), 10, 1.0, INF, 0.03,)),
+        ("general_inf", case_norm_dist_g, (60, 37, 2, 24, 20, 3, INF,)),
+        ("general_inf_hw", case_norm_dist_g, (61, 10, 1, 19, 7, 5, INF,)),
+        ("general_p8", case_norm_dist_g, (62, 37, 2, 24, 20, 3, 8.0,)),
+        ("general_p20_groups", case_norm_dist_g, (63, 21, 3, 16, 9, 1, 20.0,)),
+        ("general_dropout_inf", case_dropout_g, (64, 40, 2, 30, 26, 3, 0.8, INF,)),
+        ("general_dropout_p8", case_dropout_g, (65, 40, 2, 30, 26, 3, 0.8, 8.0,)),
+        ("general_bound", case_bound_g, (66, 37, 2, 24, 20, 3, 0.1,)),
+        ("general_sort", case_sort_g, (67, 12, 2, 24, 8, 3, 0.6, 6,)),
+    ]
+    for name, fn, args in cases:
+        if not want or any(name.startswith(p) for p in want):
+            save(name, fn(*args))
 
 if __name__ == "__main__":
     main()
