@@ -9,13 +9,19 @@
  *
  * Conventions
  *   - All pointers are device pointers to contiguous fp32 / int32 arrays owned by the
- *     caller; nothing is allocated or freed here.  Outputs are overwritten; gradient
+ *     caller; the 2-D shapes (G == 1, HW == 1) allocate and free nothing.  Outputs are overwritten; gradient
  *     buffers are zero-filled by the backward entry points before they scatter into them
  *     (the reference launchers do the same, e.g. inf_dist_cuda.cu:332,348-349).
- *   - Shapes: x [B, CI, HW], w [W_CO, W_CI / G], y [B, CO, HW].  Only G == 1 and HW == 1
- *     are implemented (every fully connected SortNet layer); anything else returns
- *     SNB_STATUS_UNSUPPORTED.
- *   - Index lists (`w_index_ci` [S, CI], `w_index_co` [S, CO], S = ceil(B / 32), sorted
+ *   - Shapes: x [B, CI, HW], w [W_CO, W_CI / G], y [B, CO, HW]; CO, CI, W_CO and W_CI are totals
+ *     over the G groups (W_CI = columns of w times G, as core/cuda/norm_dist.cpp:139-143 passes
+ *     it).  Group g of the outputs sees input channels g*CI/G .. (g+1)*CI/G - 1 and rows
+ *     g*W_CO/G .. of w; the HW positions of a row are independent samples that share the row's
+ *     sub-batch (inf_dist_cuda.cu:112-123,152-171).  G == 1 and HW == 1 (every fully connected
+ *     SortNet layer) run the tiled kernels directly.  Any other G >= 1, HW >= 1 is served by
+ *     repacking the operands into G row-major 2-D problems, running the same kernels on each and
+ *     scattering the results back; that path takes its scratch from the stream-ordered allocator
+ *     (cudaMallocAsync / cudaFreeAsync on `stream`), about two copies of the operands.
+ *   - Index lists (`w_index_ci` [S, G, CI / G], `w_index_co` [S, G, CO / G], S = ceil(B / 32),
  *     int32, may be NULL) select, for each 32-row sub-batch, the columns / rows of w that the
  *     compact x / y correspond to (core/models/norm_dist.py:14-17; inf_dist_cuda.cu:123,166-169).
  *   - `stream` is a cudaStream_t (NULL = legacy default stream).  Work is enqueued on it and

@@ -11,6 +11,7 @@
 #include <stdlib.h>
 #include "tile.cuh"
 #include "launch.h"
+#include "general_shapes.h"
 
 namespace snb {
 
@@ -357,6 +358,8 @@ static int check_bound(const void* xl, const void* xu, const void* w, const void
 extern "C" int snb_bound_inf_dist_forward_nograd(const float* xl, const float* xu, const float* w,
                                                  int B, int CO, int CI, int G, int HW, float* yl,
                                                  float* yu, void* stream) {
+    if (G != 1 || HW != 1)
+        return general_bound_forward(xl, xu, w, B, CO, CI, G, HW, yl, yu, nullptr, nullptr, (cudaStream_t)stream);
     int rc = check_bound(xl, xu, w, yl, yu, B, CO, CI, G, HW);
     if (rc) return rc;
     BoundParams p{xl, xu, w, yl, yu, nullptr, nullptr, B, CO, CI, 0, 0, 0};
@@ -379,6 +382,10 @@ extern "C" int snb_bound_inf_dist_forward_nograd(const float* xl, const float* x
 extern "C" int snb_bound_inf_dist_forward(const float* xl, const float* xu, const float* w, int B,
                                           int CO, int CI, int G, int HW, float* yl, float* yu,
                                           int* posl, int* posu, void* stream) {
+    if (G != 1 || HW != 1) {
+        if (!posl || !posu) return SNB_ERR_NULL_POINTER;
+        return general_bound_forward(xl, xu, w, B, CO, CI, G, HW, yl, yu, posl, posu, (cudaStream_t)stream);
+    }
     int rc = check_bound(xl, xu, w, yl, yu, B, CO, CI, G, HW);
     if (rc) return rc;
     if (!posl || !posu) return SNB_ERR_NULL_POINTER;
@@ -403,8 +410,9 @@ extern "C" int snb_bound_inf_dist_forward(const float* xl, const float* xu, cons
 static int bound_backward(const float* gl, const float* gu, const int* posl, const int* posu, int B,
                           int CO, int CI, int G, int HW, float* gxl, float* gxu, float* gw,
                           cudaStream_t st) {
+    if (G != 1 || HW != 1)
+        return general_bound_backward(gl, gu, posl, posu, B, CO, CI, G, HW, gxl, gxu, gw, st);
     if (!gl || !gu || !posl || !posu || !gxl || !gxu) return SNB_ERR_NULL_POINTER;
-    if (G != 1 || HW != 1) return SNB_ERR_UNSUPPORTED;
     if (B <= 0 || CO <= 0 || CI <= 0) return SNB_ERR_BAD_SHAPE;
     if ((long long)CO * CI >= (1ll << 31)) return SNB_ERR_TOO_LARGE;
     if (gw) SNB_CUDA(cudaMemsetAsync(gw, 0, sizeof(float) * (size_t)CO * CI, st));

@@ -13,7 +13,7 @@ enum {
     SNB_OK = 0,
     SNB_ERR_NULL_POINTER = 1,
     SNB_ERR_BAD_SHAPE = 2,
-    SNB_ERR_UNSUPPORTED = 3,      // G != 1 or HW != 1, or a p outside (0, inf)
+    SNB_ERR_UNSUPPORTED = 3,      // a p outside (0, inf), a sort size outside 2..25, groups without scratch
     SNB_ERR_TOO_LARGE = 4,        // an index would not fit 31 bits
     SNB_ERR_CUDA = 5,             // a CUDA runtime call failed (see snb_last_cuda_error)
     SNB_ERR_ALIGNMENT = 6,

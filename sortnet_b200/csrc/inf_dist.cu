@@ -15,6 +15,7 @@
 // inside the chunk is the same total order as the reference's strict '>' element scan.
 #include "tile.cuh"
 #include "launch.h"
+#include "general_shapes.h"
 
 #ifndef SNB_LINF_FORM
 #define SNB_LINF_FORM 0
@@ -425,6 +426,8 @@ static int check_fwd(const void* x, const void* w, const void* y, int B, int CO,
 static int inf_forward_impl(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
                             float* y, int* pos, const int* ci, const int* co, int W_CO, int W_CI,
                             unsigned long long* keys, cudaStream_t st) {
+    if (G != 1 || HW != 1)
+        return general_inf_forward(x, w, B, CO, CI, G, HW, y, pos, ci, co, W_CO, W_CI, st);
     int rc = check_fwd(x, w, y, B, CO, CI, G, HW, W_CO, W_CI, ci, co);
     if (rc) return rc;
     if (!pos) return SNB_ERR_NULL_POINTER;
@@ -465,6 +468,9 @@ extern "C" int snb_inf_dist_forward_ws(const float* x, const float* w, int B, in
 
 extern "C" int snb_inf_dist_forward_nograd(const float* x, const float* w, int B, int CO, int CI,
                                            int G, int HW, float* y, void* stream) {
+    if (G != 1 || HW != 1)
+        return general_inf_forward(x, w, B, CO, CI, G, HW, y, nullptr, nullptr, nullptr, CO, CI,
+                                   (cudaStream_t)stream);
     int rc = check_fwd(x, w, y, B, CO, CI, G, HW, CO, CI, nullptr, nullptr);
     if (rc) return rc;
     InfFwdParams p{x, w, y, nullptr, nullptr, nullptr, B, CO, CI, CI};
@@ -500,6 +506,7 @@ static cudaError_t noalloc_keys_address(unsigned long long** out) {
 
 extern "C" int snb_inf_dist_forward_noalloc(const float* x, const float* w, int B, int CO, int CI,
                                             int G, int HW, float* y, int* pos, void* stream) {
+    if (G != 1 || HW != 1) return SNB_ERR_UNSUPPORTED;  // the general shapes take scratch from an allocator
     if (B > 0 && CO > 0 && (long long)B * CO > SNB_NOALLOC_MAX_OUTPUTS) return SNB_ERR_STATIC_CAPACITY;
     unsigned long long* keys = nullptr;
     SNB_CUDA(noalloc_keys_address(&keys));
@@ -514,8 +521,9 @@ extern "C" int snb_inf_dist_forward_noalloc_max_outputs(void) { return SNB_NOALL
 static int inf_backward(const float* g, const int* pos, int B, int CO, int CI, int G, int HW,
                         float* gx, float* gw, const int* ci, const int* co, int W_CO, int W_CI,
                         cudaStream_t st) {
+    if (G != 1 || HW != 1)
+        return general_inf_backward(g, pos, B, CO, CI, G, HW, gx, gw, ci, co, W_CO, W_CI, st);
     if (!g || !pos || !gx) return SNB_ERR_NULL_POINTER;
-    if (G != 1 || HW != 1) return SNB_ERR_UNSUPPORTED;
     if (B <= 0 || CO <= 0 || CI <= 0) return SNB_ERR_BAD_SHAPE;
     if (gw) {
         if (W_CO <= 0 || W_CI <= 0 || (!ci && W_CI != CI) || (!co && W_CO != CO)) return SNB_ERR_BAD_SHAPE;

@@ -18,6 +18,7 @@
 #include <float.h>
 #include "tile.cuh"
 #include "launch.h"
+#include "general_shapes.h"
 
 namespace snb {
 
@@ -494,8 +495,11 @@ using namespace snb;
 extern "C" int snb_norm_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G,
                                      int HW, float* y, float p, const int* w_index_ci,
                                      const int* w_index_co, int W_CO, int W_CI, void* stream) {
+    if (!(p > 0) || isinf(p)) return SNB_ERR_UNSUPPORTED;
+    if (G != 1 || HW != 1)
+        return general_lp_forward(x, w, B, CO, CI, G, HW, y, p, w_index_ci, w_index_co, W_CO, W_CI,
+                                  (cudaStream_t)stream);
     if (!x || !w || !y) return SNB_ERR_NULL_POINTER;
-    if (G != 1 || HW != 1 || !(p > 0) || isinf(p)) return SNB_ERR_UNSUPPORTED;
     if (B <= 0 || CO <= 0 || CI <= 0 || W_CO <= 0 || W_CI <= 0) return SNB_ERR_BAD_SHAPE;
     if ((!w_index_ci && W_CI != CI) || (!w_index_co && W_CO != CO) || CI > W_CI || CO > W_CO)
         return SNB_ERR_BAD_SHAPE;
@@ -525,8 +529,10 @@ extern "C" int snb_norm_dist_forward(const float* x, const float* w, int B, int 
 static int lp_backward(const float* g, const float* x, const float* w, const float* y, int B, int CO,
                        int CI, int G, int HW, float* gx, float* gw, float p, const int* ci,
                        const int* co, int W_CO, int W_CI, cudaStream_t st) {
+    if (!(p > 0) || isinf(p)) return SNB_ERR_UNSUPPORTED;
+    if (G != 1 || HW != 1)
+        return general_lp_backward(g, x, w, y, B, CO, CI, G, HW, gx, gw, p, ci, co, W_CO, W_CI, st);
     if (!g || !x || !w || !y || !gx) return SNB_ERR_NULL_POINTER;
-    if (G != 1 || HW != 1 || !(p > 0) || isinf(p)) return SNB_ERR_UNSUPPORTED;
     if (B <= 0 || CO <= 0 || CI <= 0 || W_CO <= 0 || W_CI <= 0) return SNB_ERR_BAD_SHAPE;
     if ((!ci && W_CI != CI) || (!co && W_CO != CO) || CI > W_CI || CO > W_CO) return SNB_ERR_BAD_SHAPE;
     if ((long long)W_CO * W_CI >= (1ll << 31) || (long long)B * CO >= (1ll << 31) || (long long)B * CI >= (1ll << 31))

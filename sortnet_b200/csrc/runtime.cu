@@ -28,7 +28,7 @@ extern "C" const char* snb_status_string(int status) {
         case SNB_OK: return "ok";
         case SNB_ERR_NULL_POINTER: return "null pointer argument";
         case SNB_ERR_BAD_SHAPE: return "inconsistent or non-positive sizes";
-        case SNB_ERR_UNSUPPORTED: return "unsupported configuration (only G = 1, HW = 1, 0 < p)";
+        case SNB_ERR_UNSUPPORTED: return "unsupported configuration (p outside (0, inf), sort size outside 2..25, or groups on an entry point without scratch)";
         case SNB_ERR_TOO_LARGE: return "tensor too large for 31-bit indexing";
         case SNB_ERR_CUDA: return "CUDA runtime error";
         case SNB_ERR_ALIGNMENT: return "pointer not aligned to its element type";

@@ -11,6 +11,7 @@
 // reference binary may contract multiply-adds differently), positions agree exactly.
 #include "tile.cuh"
 #include "launch.h"
+#include "general_shapes.h"
 
 namespace snb {
 
@@ -286,6 +287,8 @@ static int check_sort(const void* x, const void* w, const void* y, int B, int CO
 
 extern "C" int snb_sort_neuron_forward_nograd(const float* x, const float* w, int B, int CO, int CI, int G,
                                               int HW, float* y, float q, int K, void* stream) {
+    if ((G != 1 || HW != 1) && q > 0.f && q < 1.f)
+        return general_sort_forward(x, w, B, CO, CI, G, HW, y, nullptr, q, K, (cudaStream_t)stream);
     int rc = check_sort(x, w, y, B, CO, CI, G, HW, q, K);
     if (rc) return rc;
     SortParams p{x, x, w, y, nullptr, nullptr, B, CO, CI, K, q};
@@ -296,6 +299,10 @@ extern "C" int snb_sort_neuron_forward_nograd(const float* x, const float* w, in
 
 extern "C" int snb_sort_neuron_forward(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
                                        float* y, int* pos, float q, int K, void* stream) {
+    if ((G != 1 || HW != 1) && q > 0.f && q < 1.f) {
+        if (!pos) return SNB_ERR_NULL_POINTER;
+        return general_sort_forward(x, w, B, CO, CI, G, HW, y, pos, q, K, (cudaStream_t)stream);
+    }
     int rc = check_sort(x, w, y, B, CO, CI, G, HW, q, K);
     if (rc) return rc;
     if (!pos) return SNB_ERR_NULL_POINTER;
@@ -309,6 +316,8 @@ extern "C" int snb_sort_neuron_forward(const float* x, const float* w, int B, in
 extern "C" int snb_bound_sort_neuron_forward(const float* xl, const float* xu, const float* w, int B, int CO,
                                              int CI, int G, int HW, float* yl, float* yu, float q, int K,
                                              void* stream) {
+    if ((G != 1 || HW != 1) && q > 0.f && q < 1.f)
+        return general_sort_bound_forward(xl, xu, w, B, CO, CI, G, HW, yl, yu, q, K, (cudaStream_t)stream);
     int rc = check_sort(xl, w, yl, B, CO, CI, G, HW, q, K);
     if (rc) return rc;
     if (!xu || !yu) return SNB_ERR_NULL_POINTER;
@@ -320,6 +329,8 @@ extern "C" int snb_bound_sort_neuron_forward(const float* xl, const float* xu, c
 
 static int sort_backward(const float* g, const int* pos, int B, int CO, int CI, int G, int HW, float* gx,
                          float* gw, float q, int K, cudaStream_t st) {
+    if ((G != 1 || HW != 1) && q > 0.f && q < 1.f)
+        return general_sort_backward(g, pos, B, CO, CI, G, HW, gx, gw, q, K, st);
     if (!g || !pos || !gx) return SNB_ERR_NULL_POINTER;
     if (G != 1 || HW != 1 || K < 2 || K > 25 || !(q > 0.f) || !(q < 1.f)) return SNB_ERR_UNSUPPORTED;
     if (B <= 0 || CO <= 0 || CI <= 0) return SNB_ERR_BAD_SHAPE;

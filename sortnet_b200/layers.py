@@ -8,6 +8,7 @@ What is mirrored from the reference
     NormDist             core/models/norm_dist.py:20-121  (parameters `weight` [CO, CI], `bias`;
                          std / identity initialisation; attribute `p`; returns the triple
                          (x, lower, upper))
+    NormDistConv         core/models/norm_dist.py:130-164  (unfold + grouped distance, 4-D in/out)
     SortMLPModel         ell_inf_models.py:17-50           (layer stack, forward signature, margin)
 so a reference checkpoint's state_dict loads into SortMLPModel unchanged.
 
@@ -20,6 +21,7 @@ import math
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from . import norm_dist_cuda as _C
 from . import ops
@@ -44,6 +46,57 @@ def _as_index32(index):
     if index.dtype != torch.int32:
         index = index.int()
     return index.contiguous()
+
+
+def _global_index(index, channels):
+    """[S, G, kept per group] lists of within-group channels -> [S, G * kept] lists of channels
+    of the whole layer (group g owns channels g * channels / G ...), still ascending."""
+    S, G, kept = index.shape
+    base = torch.arange(G, device=index.device, dtype=torch.long).view(1, G, 1) * (channels // G)
+    return (index.long() + base).reshape(S, G * kept)
+
+
+def _plane_index(index, channels, hw):
+    """Index lists over the flattened (channel, position) plane of a [B, C, HW] tensor, in the
+    [S, 1, n] int32 form the mean-shift kernels take; None stays None."""
+    if index is None:
+        return None
+    glob = _global_index(index, channels)
+    if hw > 1:
+        glob = (glob.unsqueeze(-1) * hw + torch.arange(hw, device=glob.device)).reshape(glob.size(0), -1)
+    return glob.int().unsqueeze(1).contiguous()
+
+
+class _MeanShiftPlaneF(torch.autograd.Function):
+    """The centring of _MeanShiftTrainF for x [B, C, HW] and grouped index lists
+    (core/models/bound_basic_module.py:125-139: the mean runs over rows and positions).  The
+    statistics kernel sees the (channel, position) plane as one long channel axis; every
+    position of a channel has the same row count, so the channel mean is the plain average of
+    its per-position means."""
+
+    @staticmethod
+    def forward(ctx, x, plane_index, channels):
+        B, hw = x.size(0), x.size(-1)
+        flat = x.contiguous().view(B, -1, 1)
+        per_pos = torch.empty(channels * hw, device=x.device, dtype=torch.float32)
+        _C.mean_shift_stats(flat, plane_index, per_pos, None, 0.0)
+        mean = per_pos.view(channels, hw).mean(dim=1)
+        y = torch.empty_like(flat)
+        _C.mean_shift_apply(flat, mean.repeat_interleave(hw), plane_index, y)
+        ctx.plane_index, ctx.channels = plane_index, channels
+        ctx.mark_non_differentiable(mean)
+        return y.view(x.shape), mean
+
+    @staticmethod
+    def backward(ctx, grad_y, _grad_mean):
+        B, hw = grad_y.size(0), grad_y.size(-1)
+        flat = grad_y.contiguous().view(B, -1, 1)
+        per_pos = torch.empty(ctx.channels * hw, device=grad_y.device, dtype=torch.float32)
+        _C.mean_shift_stats(flat, ctx.plane_index, per_pos, None, 0.0)
+        gmean = per_pos.view(ctx.channels, hw).mean(dim=1)
+        grad_x = torch.empty_like(flat)
+        _C.mean_shift_apply(flat, gmean.repeat_interleave(hw), ctx.plane_index, grad_x)
+        return grad_x.view(grad_y.shape), None, None
 
 
 class _MeanShiftTrainF(torch.autograd.Function):
@@ -87,11 +140,21 @@ class MeanShiftDropout(nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, x=None, lower=None, upper=None, index=None):
-        """x, lower, upper: (B, C, 1) or None; index: kept channels [S, 1, C] or None."""
+        """x, lower, upper: (B, C, HW) or None; index: kept channels [S, groups, C / groups] (sorted
+        within each group) or None."""
         index = _as_index32(index)
+        some = x if x is not None else lower
+        hw = some.size(-1)
+        plane = hw != 1 or (index is not None and index.size(1) != 1)
+        kernel_index = _plane_index(index, self.out_channels, hw) if plane else index
         if self.training:
             assert x is not None, "training needs the activations"
-            x, mean = _MeanShiftTrainF.apply(x, index, self.running_mean, self.momentum)
+            if plane:
+                x, mean = _MeanShiftPlaneF.apply(x, kernel_index, self.out_channels)
+                with torch.no_grad():
+                    self.running_mean.mul_(1 - self.momentum).add_(mean, alpha=self.momentum)
+            else:
+                x, mean = _MeanShiftTrainF.apply(x, index, self.running_mean, self.momentum)
             if self.bias is not None:
                 x = x + self._gathered(self.bias, index, x.size(0)).unsqueeze(-1)
                 mean = mean - self.bias.detach()
@@ -99,6 +162,8 @@ class MeanShiftDropout(nn.Module):
         else:
             mean = self.running_mean if self.bias is None else self.running_mean - self.bias.detach()
             x_done, todo = None, (x, lower, upper)
+        if plane and hw > 1:
+            mean = mean.repeat_interleave(hw)
         outs = []
         for z in todo:
             if z is None:
@@ -106,7 +171,10 @@ class MeanShiftDropout(nn.Module):
                 continue
             z = z.contiguous()
             out = torch.empty_like(z)
-            _C.mean_shift_apply(z, mean, index, out)
+            if plane:
+                _C.mean_shift_apply(z.view(z.size(0), -1, 1), mean, kernel_index, out.view(z.size(0), -1, 1))
+            else:
+                _C.mean_shift_apply(z, mean, index, out)
             outs.append(out)
         if x_done is not None:
             outs[0] = x_done
@@ -114,10 +182,11 @@ class MeanShiftDropout(nn.Module):
 
     @staticmethod
     def _gathered(vec, index, batch):
+        """vec [C_full] -> [batch or 1, C]: the entries of the channels each row's sub-batch kept."""
         if index is None:
             return vec.unsqueeze(0)
         rows = torch.arange(batch, device=vec.device) // SUB_BATCH
-        return vec[index[rows, 0].long()]
+        return vec[_global_index(index, vec.numel())[rows]]
 
     def extra_repr(self):
         return "{}, affine={}".format(self.out_channels, self.affine)
@@ -177,6 +246,77 @@ class NormDist(nn.Module):
     def extra_repr(self):
         return "in_features={}, out_features={}, bias={}, keep={}".format(
             self.in_features, self.out_features, self.bias is not None, self.dropout)
+
+
+class NormDistConv(nn.Module):
+    """Convolutional norm-distance layer (core/models/norm_dist.py:130-164): every output pixel
+    is the distance between the unfolded input patch and a weight row, per channel group.
+
+    Parameters as in the reference: `weight` [out_channels, in_channels / groups * kh * kw],
+    optional `bias` [out_channels], `mean_shift.running_mean`.  Inputs and outputs are 4-D
+    (B, C, H, W).  With masks (training of the sort-neuron estimate) the input must already be
+    compact over `mask_in` [S, groups, kept]; that is the case between 1x1 layers, whose compact
+    output over `mask_out` is the next layer's compact input."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1,
+                 p=float("inf"), bias=True, std=1.0, mean_shift=True, dropout=None, identity_val=None):
+        super().__init__()
+        if not isinstance(kernel_size, (tuple, list)):
+            kernel_size = (kernel_size, kernel_size)
+        kernel_size = tuple(kernel_size)
+        assert in_channels % groups == 0 and out_channels % groups == 0
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding, self.dilation = kernel_size, stride, padding, dilation
+        self.groups, self.p, self.dropout = groups, p, dropout
+        fan_in = in_channels // groups * kernel_size[0] * kernel_size[1]
+        self.weight = nn.Parameter(torch.randn(out_channels, fan_in) * std)
+        self.bias = nn.Parameter(torch.zeros(out_channels)) if bias else None
+        self.mean_shift = MeanShiftDropout(out_channels, affine=False) if mean_shift else None
+        if identity_val is not None and in_channels <= out_channels:
+            with torch.no_grad():
+                w4 = self.weight.view(out_channels, -1, *kernel_size)
+                rows = torch.arange(out_channels)
+                w4[rows, rows % (in_channels // groups), kernel_size[0] // 2, kernel_size[1] // 2] = -identity_val
+
+    @property
+    def keep_rate(self):
+        return 1.0 if self.dropout is None else self.dropout
+
+    def _unfold(self, z):
+        if z is None:
+            return None
+        if self.kernel_size == (1, 1) and self.stride == 1 and self.padding == 0:
+            return z.reshape(z.size(0), z.size(1), -1).contiguous()
+        return F.unfold(z, self.kernel_size, self.dilation, self.padding, self.stride).contiguous()
+
+    def forward(self, x=None, lower=None, upper=None, mask_in=None, mask_out=None, sort_eval=False):
+        some = x if x is not None else lower
+        h, w = ((n + 2 * self.padding - self.dilation * (k - 1) - 1) // self.stride + 1
+                for n, k in zip(some.shape[2:], self.kernel_size))
+        x3, l3, u3 = self._unfold(x), self._unfold(lower), self._unfold(upper)
+        if mask_in is not None or mask_out is not None:
+            x3 = ops.norm_dist_dropout(x3, self.weight, mask_in, mask_out, self.p, self.groups)
+        elif not sort_eval:
+            if x3 is not None:
+                x3 = ops.norm_dist(x3, self.weight, self.p, self.groups)
+            if l3 is not None and u3 is not None:
+                assert math.isinf(self.p)
+                l3, u3 = ops.bound_inf_dist(l3, u3, self.weight, self.groups)
+        else:
+            x3 = ops.sort_neuron(x3, self.weight, self.groups, q=self.dropout)
+            if l3 is not None and u3 is not None:
+                l3, u3 = ops.bound_sort_neuron(l3, u3, self.weight, self.groups, q=self.dropout)
+        if self.mean_shift is not None:
+            x3, l3, u3 = self.mean_shift(x3, l3, u3, index=mask_out)
+        if self.bias is not None:
+            b = MeanShiftDropout._gathered(self.bias, mask_out, some.size(0)).unsqueeze(-1)
+            x3, l3, u3 = (None if z is None else z + b for z in (x3, l3, u3))
+        return tuple(None if z is None else z.view(z.size(0), -1, h, w) for z in (x3, l3, u3))
+
+    def extra_repr(self):
+        return "{}, {}, kernel_size={}, stride={}, groups={}, bias={}, keep={}".format(
+            self.in_channels, self.out_channels, self.kernel_size, self.stride, self.groups,
+            self.bias is not None, self.dropout)
 
 
 class SortMLPModel(nn.Module):

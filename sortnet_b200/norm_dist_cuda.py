@@ -28,12 +28,14 @@ def _check(t, name, dtype=torch.float32):
         raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
 
 
-def _check_opt_index(t, name, n_sub, width):
+def _check_opt_index(t, name, n_sub, width, groups=1):
+    """Index lists are [sub-batches, groups, kept channels per group]; `width` is the total over groups."""
     if t is None:
         return
     _check(t, name, torch.int32)
-    if t.dim() != 3 or t.size(0) != n_sub or t.size(1) != 1 or t.size(2) != width:
-        raise RuntimeError("%s must have shape [%d, 1, %d], got %s" % (name, n_sub, width, tuple(t.shape)))
+    if t.dim() != 3 or t.size(0) != n_sub or t.size(1) != groups or t.size(2) * groups != width:
+        raise RuntimeError("%s must have shape [%d, %d, %d], got %s"
+                           % (name, n_sub, groups, width // max(groups, 1), tuple(t.shape)))
 
 
 def _ptr(t):
@@ -115,8 +117,8 @@ def inf_dist_forward(input, weight, output, pos, G, w_index_ci=None, w_index_co=
     _check(pos, "pos", torch.int32)
     B, CO, CI, HW = _dims(input, output)
     S = (B + _SUB_BATCH - 1) // _SUB_BATCH
-    _check_opt_index(w_index_ci, "w_index_ci", S, CI)
-    _check_opt_index(w_index_co, "w_index_co", S, CO)
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G)
+    _check_opt_index(w_index_co, "w_index_co", S, CO, G)
     if output.size(0) != B or pos.shape != output.shape:
         raise RuntimeError("output / pos shape mismatch")
     dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
@@ -157,8 +159,8 @@ def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
     _check(grad_input, "grad_input"); _check(grad_weight, "grad_weight")
     B, CO, CI, HW = grad_output.size(0), grad_output.size(1), grad_input.size(1), grad_output.size(2)
     S = (B + _SUB_BATCH - 1) // _SUB_BATCH
-    _check_opt_index(w_index_ci, "w_index_ci", S, CI)
-    _check_opt_index(w_index_co, "w_index_co", S, CO)
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G)
+    _check_opt_index(w_index_co, "w_index_co", S, CO, G)
     if pos.shape != grad_output.shape or grad_input.size(0) != B:
         raise RuntimeError("shape mismatch between grad_output, pos and grad_input")
     dev = _same_device(grad_output, pos, grad_input, grad_weight, w_index_ci, w_index_co)
@@ -167,18 +169,18 @@ def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
           _ptr(w_index_ci), _ptr(w_index_co), grad_weight.size(0), grad_weight.size(1) * G)
 
 
-def _lp_common(input, weight, output, w_index_ci, w_index_co):
+def _lp_common(input, weight, output, w_index_ci, w_index_co, G):
     B, CO, CI, HW = _dims(input, output)
     S = (B + _SUB_BATCH - 1) // _SUB_BATCH
-    _check_opt_index(w_index_ci, "w_index_ci", S, CI)
-    _check_opt_index(w_index_co, "w_index_co", S, CO)
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G)
+    _check_opt_index(w_index_co, "w_index_co", S, CO, G)
     return B, CO, CI, HW
 
 
 def norm_dist_forward(input, weight, output, G, p, w_index_ci=None, w_index_co=None):
     """core/cuda/norm_dist.cpp:43-65 (p <= 10 plain sum, p > 10 max-normalised)."""
     _check(input, "input"); _check(weight, "weight"); _check(output, "output")
-    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
+    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co, G)
     dev = _same_device(input, weight, output, w_index_ci, w_index_co)
     _call(dev, input, "snb_norm_dist_forward", (B, CO, CI),
           _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), float(p), _ptr(w_index_ci),
@@ -198,7 +200,7 @@ def norm_dist_backward_input(grad_output, input, weight, output, grad_input, G, 
     for t, n in ((grad_output, "grad_output"), (input, "input"), (weight, "weight"), (output, "output"),
                  (grad_input, "grad_input")):
         _check(t, n)
-    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
+    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co, G)
     dev = _same_device(grad_output, input, weight, output, grad_input, w_index_ci, w_index_co)
     _call(dev, input, "snb_norm_dist_backward_input", (B, CO, CI),
           _ptr(grad_output), _ptr(input), _ptr(weight), _ptr(output), B, CO, CI, G, HW, _ptr(grad_input),
@@ -211,7 +213,7 @@ def norm_dist_backward_input_weight(grad_output, input, weight, output, grad_inp
     for t, n in ((grad_output, "grad_output"), (input, "input"), (weight, "weight"), (output, "output"),
                  (grad_input, "grad_input"), (grad_weight, "grad_weight")):
         _check(t, n)
-    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co)
+    B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co, G)
     if grad_weight.shape != weight.shape:
         raise RuntimeError("grad_weight must have the shape of weight")
     dev = _same_device(grad_output, input, weight, output, grad_input, grad_weight, w_index_ci, w_index_co)

@@ -281,6 +281,76 @@ def case_sort_g(seed, B, G, CIg, COg, HW, q, K):
                 gx=xp.grad, gw=wp.grad)
 
 
+def case_conv_stack(seed, B, q, p):
+    """Three of the reference's NormDistConv layers (3x3 grouped, then two 1x1) run through its
+    PyTorch branches: training forward/backward (masked when q < 1), then evaluation (sort neurons
+    when q < 1; interval bounds when q == 1 and p == inf)."""
+    ref_layers = sys.modules["core.models.norm_dist"]
+    ref_layers.NormDistBase.dropout_list = dict()
+    ref_layers.NormDistBase.dropout_buffer = None
+    ref_layers.NormDistBase.tag = 0
+    torch.manual_seed(seed)
+    drop = None if q == 1.0 else q
+    G = 2
+    layers = [ref_layers.NormDistConv(4, 12, 3, stride=1, groups=G, bias=False, mean_shift=True, p=p),
+              ref_layers.NormDistConv(12, 12, 1, groups=G, bias=True, mean_shift=True, dropout=drop, p=p),
+              ref_layers.NormDistConv(12, 8, 1, groups=G, bias=True, mean_shift=False, dropout=drop, p=p)]
+    with torch.no_grad():
+        for l in layers:
+            if l.bias is not None:
+                l.bias.normal_()
+    S = (B - 1) // 32 + 1
+    masks = [sample_mask(S, G, 6, q, device="cpu").sort(dim=-1)[0] for _ in range(2)] if drop else []
+    feed = iter(masks)
+    saved = {n: getattr(ref_layers, n) for n in ("sample_mask", "norm_dist", "norm_dist_dropout",
+                                                  "bound_inf_dist", "sort_neuron")}
+    saved_ops = ref_ops.norm_dist
+    ref_layers.sample_mask = lambda *a, **k: next(feed)
+    ref_ops.norm_dist = functools.partial(saved_ops, use_custom_cuda_func=False)
+    for n in ("norm_dist", "norm_dist_dropout", "bound_inf_dist", "sort_neuron"):
+        setattr(ref_layers, n, functools.partial(getattr(ref_ops, n), use_custom_cuda_func=False))
+    try:
+        x = torch.rand(B, 4, 5, 5)
+        gy = torch.randn(B, 8, 3, 3)
+        out = {"x": x, "gy": gy, "p": np.float64(p), "q": np.float64(q), "G": np.int64(G)}
+        for i, mk in enumerate(masks):
+            out["mask%d" % i] = mk
+        for i, l in enumerate(layers):
+            for k, v in l.state_dict().items():
+                out["state0.%d.%s" % (i, k)] = v.clone()
+            l.train()
+        xp = x.clone().requires_grad_()
+        z = (xp, None, None)
+        for l in layers:
+            z = l(*z)
+        z[0].backward(gy)
+        out.update(y=z[0].detach(), gx=xp.grad)
+        for i, l in enumerate(layers):
+            for k, prm in l.named_parameters():
+                out["grad.%d.%s" % (i, k)] = prm.grad
+            if l.mean_shift is not None:
+                out["state1.%d.mean_shift.running_mean" % i] = l.mean_shift.running_mean.clone()
+            l.eval()
+        with torch.no_grad():
+            if drop is None and math.isinf(p):
+                z = (x, (x - 0.05).clamp(0, 1), (x + 0.05).clamp(0, 1))
+            else:
+                z = (x, None, None)
+            if math.isinf(p):
+                for l in layers:
+                    z = l(*z)
+                out["eval_y"] = z[0]
+                if z[1] is not None:
+                    out.update(eval_lower=z[1], eval_upper=z[2])
+    finally:
+        for n, f in saved.items():
+            setattr(ref_layers, n, f)
+        ref_ops.norm_dist = saved_ops
+        ref_layers.NormDistBase.dropout_list = dict()
+        ref_layers.NormDistBase.dropout_buffer = None
+    return out
+
+
 def save(name, d):
     arrs = {k: (v.detach().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in d.items()}
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **arrs)
@@ -317,6 +387,9 @@ def main():
         ("general_dropout_p8", case_dropout_g, (65, 40, 2, 30, 26, 3, 0.8, 8.0,)),
         ("general_bound", case_bound_g, (66, 37, 2, 24, 20, 3, 0.1,)),
         ("general_sort", case_sort_g, (67, 12, 2, 24, 8, 3, 0.6, 6,)),
+        ("conv_stack_masked_inf", case_conv_stack, (70, 40, 0.7, INF,)),
+        ("conv_stack_masked_p8", case_conv_stack, (71, 40, 0.7, 8.0,)),
+        ("conv_stack_plain_inf", case_conv_stack, (72, 37, 1.0, INF,)),
     ]
     for name, fn, args in cases:
         if not want or any(name.startswith(p) for p in want):

@@ -46,7 +46,8 @@ def test_status_codes_without_gpu(built_lib):
     lib = _lib.load()
     assert lib.snb_inf_dist_forward_nograd(None, None, 1, 1, 1, 1, 1, None, None) == 1
     one = ctypes.c_void_p(16)
-    assert lib.snb_inf_dist_forward_nograd(one, one, 1, 1, 1, 2, 1, one, None) == 3      # groups
+    assert lib.snb_inf_dist_forward_nograd(one, one, 1, 1, 1, 2, 1, one, None) == 2      # 1 channel, 2 groups
+    assert lib.snb_inf_dist_forward_noalloc(one, one, 2, 2, 2, 2, 1, one, one, None) == 3   # groups need scratch
     assert lib.snb_inf_dist_forward_nograd(one, one, 0, 1, 1, 1, 1, one, None) == 2      # empty batch
     assert lib.snb_inf_dist_forward(one, one, 4, 4, 4, 1, 1, one, one, None, None, 5, 4, None) == 2
     assert lib.snb_norm_dist_forward(one, one, 4, 4, 4, 1, 1, one, ctypes.c_float(-1.0), None, None, 4, 4, None) == 3
