@@ -222,3 +222,42 @@ def test_timings_against_the_reference_kernels(ref, capsys):
             print("%-48s reference %8.3f ms   this library %8.3f ms   x%.2f" % (name, t_ref, t_mine, t_ref / t_mine))
     for name, t_ref, t_mine in rows:
         assert t_mine <= 1.25 * t_ref, name
+
+
+@pytest.mark.parametrize("B,G,CIg,COg,HW,keep", [(37, 2, 24, 20, 3, None), (64, 3, 32, 48, 4, None),
+                                                 (40, 2, 30, 26, 3, 0.8), (70, 1, 19, 7, 5, 0.8)])
+def test_grouped_spatial_forward(ref, B, G, CIg, COg, HW, keep):
+    """The reference's own kernels on x [B, G*CIg, HW] (their has_hw / blockIdx.z = group paths)
+    next to the repacked path of this library: values and position words bit for bit."""
+    from sortnet_b200 import norm_dist_cuda as C
+    rng = np.random.default_rng(B + G + HW)
+    S = (B + 31) // 32
+    ci = co = None
+    if keep is not None:
+        def lists(width):
+            n = max(int((rng.random(width) < keep).sum()), 1)
+            m = np.stack([[np.sort(rng.permutation(width)[:n]) for _ in range(G)] for _ in range(S)])
+            return torch.from_numpy(m.astype(np.int32)).cuda()
+        ci, co = lists(CIg), lists(COg)
+    ci_n = CIg if ci is None else ci.size(-1)
+    co_n = COg if co is None else co.size(-1)
+    x = torch.rand(B, G * ci_n, HW, device="cuda")
+    w = torch.randn(G * COg, CIg, device="cuda")
+    y_r = torch.empty(B, G * co_n, HW, device="cuda")
+    p_r = torch.empty(B, G * co_n, HW, device="cuda", dtype=torch.int32)
+    y_m, p_m = torch.empty_like(y_r), torch.empty_like(p_r)
+    if ci is None:
+        ref.inf_dist_forward(x, w, y_r, p_r, G)
+    else:
+        ref.inf_dist_forward(x, w, y_r, p_r, G, ci, co)
+    C.inf_dist_forward(x, w, y_m, p_m, G, ci, co)
+    torch.cuda.synchronize()
+    assert torch.equal(y_r, y_m) and torch.equal(p_r, p_m)
+    if ci is None:
+        xl, xu = (x - 0.04).clamp(0, 1), (x + 0.04).clamp(0, 1)
+        outs_r = [torch.empty_like(y_r) for _ in range(2)]
+        outs_m = [torch.empty_like(y_r) for _ in range(2)]
+        ref.bound_inf_dist_forward_nograd(xl, xu, w, *outs_r, G)
+        C.bound_inf_dist_forward_nograd(xl, xu, w, *outs_m, G)
+        torch.cuda.synchronize()
+        assert torch.equal(outs_r[0], outs_m[0]) and torch.equal(outs_r[1], outs_m[1])
