@@ -140,6 +140,20 @@ int snb_norm_dist_forward(const float* x, const float* w, int B, int CO, int CI,
                           float* y, float p, const int* w_index_ci, const int* w_index_co,
                           int W_CO, int W_CI, void* stream);
 
+/* The same operation with caller-provided scratch memory for p > 10: the maxima M then live in
+ * `workspace` (snb_norm_dist_forward_workspace_bytes(B, CO, p) = 4 * B * CO bytes, 16-byte aligned,
+ * any content on entry) instead of y, which frees y to collect partial sums, so that thread blocks
+ * can share output tiles along the reduction axis and every SM gets the same amount of work
+ * whatever the shape and mask sizes.  For p <= 10 no scratch is needed (the function returns 0
+ * bytes) and both entry points behave alike; with workspace NULL or too small the p > 10 case runs
+ * one thread block per output tile.  Partial sums merge with floating-point atomics, so results
+ * of the two entry points (and of repeated calls) can differ in the last bits.
+ * No counterpart in the reference (its launcher has no scratch argument). */
+size_t snb_norm_dist_forward_workspace_bytes(int B, int CO, float p);
+int snb_norm_dist_forward_ws(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                             float* y, float p, const int* w_index_ci, const int* w_index_co,
+                             int W_CO, int W_CI, void* workspace, size_t workspace_bytes, void* stream);
+
 /* grad_input[b,c] = sum_j g[b,j] sgn(t) (|t| / y[b,j])^(p-1).
  * Replaces norm_dist<ip>::backward_input (norm_dist.h:11-13; norm_dist_cuda.cu:553-572). */
 int snb_norm_dist_backward_input(const float* grad_output, const float* x, const float* w,

@@ -21,6 +21,7 @@ SIGNATURES = {
     "snb_inf_dist_backward_input": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
     "snb_inf_dist_backward_input_weight": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
     "snb_norm_dist_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P],
+    "snb_norm_dist_forward_ws": [_P, _P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P, ctypes.c_size_t, _P],
     "snb_norm_dist_backward_input": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P],
     "snb_norm_dist_backward_input_weight": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _I, _P],
     "snb_bound_inf_dist_forward_nograd": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P],

@@ -206,6 +206,8 @@ int general_lp_forward(const float* x, const float* w, int B, int CO, int CI, in
     Arena a(st);
     size_t ox = a.reserve(words(q, CIg)), oy = a.reserve(words(q, COg));
     size_t oci = ci ? a.reserve(mask_bytes(q, CIg)) : 0, oco = co ? a.reserve(mask_bytes(q, COg)) : 0;
+    const size_t ws_bytes = snb_norm_dist_forward_workspace_bytes(q.Bp, COg, p);
+    size_t ows = a.reserve(ws_bytes);
     SNB_CUDA(a.commit());
     float *xp = a.at<float>(ox), *yp = a.at<float>(oy);
     int *cip = ci ? a.at<int>(oci) : nullptr, *cop = co ? a.at<int>(oco) : nullptr;
@@ -213,9 +215,9 @@ int general_lp_forward(const float* x, const float* w, int B, int CO, int CI, in
     if (ci) SNB_CUDA(expand(ci, cip, q, CIg, st));
     if (co) SNB_CUDA(expand(co, cop, q, COg, st));
     for (int g = 0; g < G; g++) {
-        int rc = snb_norm_dist_forward(grp(xp, q, g, CIg), w + (size_t)g * W_COg * W_CIg, q.Bp, COg, CIg, 1, 1,
-                                       grp(yp, q, g, COg), p, mgrp(cip, q, g, CIg), mgrp(cop, q, g, COg), W_COg,
-                                       W_CIg, st);
+        int rc = snb_norm_dist_forward_ws(grp(xp, q, g, CIg), w + (size_t)g * W_COg * W_CIg, q.Bp, COg, CIg, 1, 1,
+                                          grp(yp, q, g, COg), p, mgrp(cip, q, g, CIg), mgrp(cop, q, g, COg), W_COg,
+                                          W_CIg, ws_bytes ? a.at<void>(ows) : nullptr, ws_bytes, st);
         if (rc) return rc;
     }
     SNB_CUDA(unpack(yp, y, q, COg, 1, st));

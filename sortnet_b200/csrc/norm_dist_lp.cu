@@ -97,16 +97,22 @@ __device__ __forceinline__ float pow_signed(float r, float e) {
 struct LpFwdParams {
     const float* x;
     const float* w;
-    float* y;  // NORMALISED: holds M on entry
+    float* y;
+    const float* m;  // NORMALISED: the maxima M (may be y itself when direct)
     const int* ci;
     const int* co;
     int B, CO, CI, W_CI;
     float p;
+    int direct;      // 1: one CTA per output tile, finished in the kernel; 0: shared tiles, lp_finish_kernel follows
 };
 
 enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
 
-// 32 x (64 * WN) tile per CTA (one sub-batch of rows), 8x8 outputs per thread.
+// 32 x (64 * WN) output tiles (one sub-batch of rows), 8x8 outputs per thread.  The (tile, k-tile)
+// pairs of the whole problem form one sequence that is cut into gridDim.x equal ranges (see
+// StreamK), so all SMs stay busy whatever the shape and the mask sizes.  With `direct` the grid
+// has one CTA per tile and each CTA turns its sums into distances itself; otherwise every range
+// adds its partial sums into the zero-filled y with atomics and lp_finish_kernel takes the root.
 template <int WN, int MODE, int IP, bool NORMALISED>
 __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
     constexpr int BM = 32, BN = 64 * WN, NT = WN * 32;
@@ -114,8 +120,18 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
     float* xs = smem;
     float* ws = smem + 2 * BM * LDS;
     const int tid = threadIdx.x, lane = tid & 31, wn = tid >> 5, tb = lane >> 3, tj = lane & 7;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int nk = (p.CI + BK - 1) / BK;
+    const StreamK sk{(p.B + BM - 1) / BM, (p.CO + BN - 1) / BN, nk};
+    long long u, u_end;
+    sk.range(u, u_end);
+    // worth testing only when most elements qualify: at p >= 48 the cut is |t|/M < 0.56
+    const bool use_skip = NORMALISED && p.p >= 48.0f;
+    const float skip_below = exp2f(-40.0f / p.p);
+
+  while (u < u_end) {
+    const int tile = (int)(u / nk), kt_begin = (int)(u % nk);
+    const int kt_end = (int)min((long long)nk, kt_begin + (u_end - u));
+    const int m0 = (tile / sk.tiles_n) * BM, n0 = (tile % sk.tiles_n) * BN;
 
     GatherW<BN, NT> gw;
     const int* ci_s = nullptr;
@@ -123,7 +139,7 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
         const int s = m0 / SNB_SUB_BATCH;
         ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
         gw.init_rows(p.co ? p.co + (size_t)s * p.CO : nullptr, n0, p.CO, p.W_CI, tid);
-        gw.fetch_cols(ci_s, 0, p.CI, tid);
+        gw.fetch_cols(ci_s, kt_begin * BK, p.CI, tid);
     }
     auto stage = [&](int kt, int st) {
         float* xd = xs + st * BM * LDS;
@@ -148,28 +164,28 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
             acc[i][j] = 0.f;
             if (NORMALISED) {
                 const int m = m0 + tb + 4 * i, n = n0 + wn * 64 + tj + 8 * j;
-                const float mx = (m < p.B && n < p.CO) ? p.y[(size_t)m * p.CO + n] : 1.0f;
+                const float mx = (m < p.B && n < p.CO) ? p.m[(size_t)m * p.CO + n] : 1.0f;
                 rm[i][j] = 1.0f / mx;
-                acc[i][j] = pow_abs<IP>(SNB_EPS * rm[i][j], p.p);  // the (EPS / M)^p seed term
+                // the (EPS / M)^p seed term, once per output
+                if (kt_begin == 0) acc[i][j] = pow_abs<IP>(SNB_EPS * rm[i][j], p.p);
             }
         }
 
-    // worth testing only when most elements qualify: at p >= 48 the cut is |t|/M < 0.56
-    const bool use_skip = NORMALISED && p.p >= 48.0f;
-    const float skip_below = exp2f(-40.0f / p.p);
-    stage(0, 0);
+    __syncthreads();                           // everyone is done with the previous range's tiles
+    stage(kt_begin, 0);
     cp_async_commit();
-    if (MODE == MODE_GATHER && nk > 1) gw.fetch_cols(ci_s, BK, p.CI, tid);
-    for (int kt = 0; kt < nk; kt++) {
+    if (MODE == MODE_GATHER && kt_begin + 1 < kt_end) gw.fetch_cols(ci_s, (kt_begin + 1) * BK, p.CI, tid);
+    for (int kt = kt_begin; kt < kt_end; kt++) {
+        const int cur = (kt - kt_begin) & 1;
         cp_async_wait<0>();
         __syncthreads();
-        if (kt + 1 < nk) {
-            stage(kt + 1, (kt + 1) & 1);
-            if (MODE == MODE_GATHER && kt + 2 < nk) gw.fetch_cols(ci_s, (kt + 2) * BK, p.CI, tid);
+        if (kt + 1 < kt_end) {
+            stage(kt + 1, cur ^ 1);
+            if (MODE == MODE_GATHER && kt + 2 < kt_end) gw.fetch_cols(ci_s, (kt + 2) * BK, p.CI, tid);
         }
         cp_async_commit();
-        const float* xr = xs + (kt & 1) * BM * LDS + tb * LDS;
-        const float* wr = ws + (kt & 1) * BN * LDS + (wn * 64 + tj) * LDS;
+        const float* xr = xs + cur * BM * LDS + tb * LDS;
+        const float* wr = ws + cur * BN * LDS + (wn * 64 + tj) * LDS;
         // zero-filled padding (x = w = 0) contributes |0|^p = 0 for every p > 0
 #pragma unroll 2
         for (int kk = 0; kk < BK / 2; kk++) {
@@ -216,11 +232,26 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
         for (int j = 0; j < 8; j++) {
             const int n = n0 + wn * 64 + tj + 8 * j;
             if (n >= p.CO) continue;
+            float* dst = p.y + (size_t)m * p.CO + n;
+            if (!p.direct) {
+                atomicAdd(dst, acc[i][j]);
+                continue;
+            }
             float r;
             if (NORMALISED) r = pow_pos(acc[i][j], rp) / rm[i][j];
             else r = pow_pos(fmaxf(acc[i][j], FLT_MIN), rp);
-            p.y[(size_t)m * p.CO + n] = r;
+            *dst = r;
         }
+    }
+    u += kt_end - kt_begin;
+  }
+}
+
+// Sums -> distances after a shared-tile forward: y = M * S^(1/p) or max(S, FLT_MIN)^(1/p).
+__global__ void lp_finish_kernel(float* __restrict__ y, const float* __restrict__ m, long long n, float rp) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float sum = y[i];
+        y[i] = m ? pow_pos(sum, rp) * m[i] : pow_pos(fmaxf(sum, FLT_MIN), rp);
     }
 }
 
@@ -237,15 +268,19 @@ struct LpBwdParams {
     float pm1;  // p - 1
 };
 
-// One CTA (NT threads) = one 32-row sub-batch x NT compact input columns; it walks all outputs j in tiles
-// of 32.  Thread (tb, tc): rows tb*8 .. tb*8+7, columns 4*tc .. 4*tc+3; the four tb lanes that
-// share tc sit in one warp (lane = (tc % 8) * 4 + tb), so the per-(j, c) sums over the 32 rows
-// finish with two shuffles and one global reduction.  The gathered W tile [32 j][NT c] and the
-// (g, y) tile of the next j-tile are fetched with cp.async while the current one is consumed.
+// Work unit: one 32-row sub-batch x NT compact input columns x one tile of 32 outputs j.  The units
+// of the whole problem form one sequence (sub-batch, column tile, j tile) that is cut into
+// gridDim.x equal ranges, so every CTA does the same amount of work whatever the shape; a range
+// that covers all j tiles of a (sub-batch, column tile) pair stores its grad_x block, a partial one
+// adds it with atomics into the zero-filled grad_x.  Thread (tb, tc): rows tb*8 .. tb*8+7,
+// columns 4*tc .. 4*tc+3; the four tb lanes that share tc sit in one warp (lane = (tc % 8) * 4 +
+// tb), so the per-(j, c) sums over the 32 rows finish with two shuffles and one global reduction.
+// The gathered W tile [32 j][NT c] and the (g, y) tile of the next j tile are fetched with
+// cp.async while the current one is consumed.
 constexpr int LPB_JT = 32;
 
 template <int IP, int NT>
-__global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
+__global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpBwdParams p) {
     constexpr int LPB_WLD = NT + 4;  // floats per W-tile row (+4: keeps 16-byte alignment, shifts banks)
     extern __shared__ __align__(16) float smem[];
     float* wt = smem;                                   // [2][JT][WLD]
@@ -253,11 +288,22 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
     float* yt = gt + 2 * LPB_JT * 33;                   // [2][JT][33]  y, turned into 1/y in place
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tb = lane & 3, tc = warp * 8 + (lane >> 2);
-    const int s = blockIdx.x, b0 = s * SNB_SUB_BATCH;
-    const int c0 = blockIdx.y * NT + tc * 4;
+    const int ntiles = (p.CO + LPB_JT - 1) / LPB_JT;
+    const int col_tiles = (p.CI + NT - 1) / NT;
+    const long long total = (long long)((p.B + SNB_SUB_BATCH - 1) / SNB_SUB_BATCH) * col_tiles * ntiles;
+    long long u = total * blockIdx.x / gridDim.x;
+    const long long u_end = total * (blockIdx.x + 1) / gridDim.x;
+    // |u|^(p-1) < 2^-40 for a whole warp: the terms are dropped (the largest terms are ~1)
+    const bool use_skip = p.pm1 >= 48.0f;
+    const float skip_below = IP < 0 ? exp2f(-40.0f / fmaxf(p.pm1, 1e-3f)) : 0.f;
+
+  while (u < u_end) {
+    const int unit = (int)(u / ntiles), t_begin = (int)(u % ntiles);
+    const int t_end = (int)min((long long)ntiles, t_begin + (u_end - u));
+    const int s = unit / col_tiles, b0 = s * SNB_SUB_BATCH;
+    const int c0 = (unit % col_tiles) * NT + tc * 4;
     const int* ci_s = p.ci ? p.ci + (size_t)s * p.CI : nullptr;
     const int* co_s = p.co ? p.co + (size_t)s * p.CO : nullptr;
-
     int col[4];
     float xv[8][4], gx[8][4];
 #pragma unroll
@@ -272,10 +318,6 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
         }
 
     const int mycol = tb == 0 ? col[0] : tb == 1 ? col[1] : tb == 2 ? col[2] : col[3];
-    const int ntiles = (p.CO + LPB_JT - 1) / LPB_JT;
-    // |u|^(p-1) < 2^-40 for a whole warp: the terms are dropped (the largest terms are ~1)
-    const bool use_skip = p.pm1 >= 48.0f;
-    const float skip_below = IP < 0 ? exp2f(-40.0f / fmaxf(p.pm1, 1e-3f)) : 0.f;
     // this thread stages rows jj = tb, tb + 4, ... of the W tile (its own four columns) and
     // elements e = tid, tid + NT, ... of the 32 x 32 (g, y) tiles
     auto stage = [&](int t, int st) {
@@ -304,13 +346,14 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
         }
     };
 
-    stage(0, 0);
+    __syncthreads();                           // everyone is done with the previous range's tiles
+    stage(t_begin, 0);
     cp_async_commit();
-    for (int t = 0; t < ntiles; t++) {
-        const int st = t & 1;
+    for (int t = t_begin; t < t_end; t++) {
+        const int st = (t - t_begin) & 1;
         cp_async_wait<0>();
         __syncthreads();                       // tile t landed; everyone is done with tile t - 1
-        if (t + 1 < ntiles) stage(t + 1, st ^ 1);
+        if (t + 1 < t_end) stage(t + 1, st ^ 1);
         cp_async_commit();
 #pragma unroll
         for (int r = 0; r < 1024 / NT; r++) {  // y -> 1/y (0 for padding), each thread its own elements
@@ -345,25 +388,25 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
                 }
             } else {
                 // general exponent: 16 terms at a time so that their log2 / exp2 chains overlap;
-                // one vote per batch for "all negligible" and one for "some ratio is near 1"
+                // one vote per batch for "all negligible" and one for "some ratio is near 1".
+                // |t| <= max_c |t| <= y, so a ratio is near 1 exactly when it is >= 0.875 and the
+                // largest ratio of the batch answers both questions.
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     float u[4][4], lg[4][4], big = 0.f;
-                    bool near = false;
 #pragma unroll
                     for (int ii = 0; ii < 4; ii++) {
                         const float ry = yp[4 * h + ii];
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
                             u[ii][k] = (xv[4 * h + ii][k] - wv[k]) * ry;
-                            const float a = fabsf(u[ii][k]);
-                            big = fmaxf(big, a);
-                            near = near || near_one(a);
-                            lg[ii][k] = lg2_approx(a);
+                            lg[ii][k] = lg2_approx(fabsf(u[ii][k]));
                         }
+#pragma unroll
+                        for (int k = 0; k < 4; k += 2) big = max3abs(big, u[ii][k], u[ii][k + 1]);
                     }
                     if (use_skip && __all_sync(0xffffffffu, big < skip_below)) continue;
-                    if (__any_sync(0xffffffffu, near)) {
+                    if (__any_sync(0xffffffffu, big >= 0.875f)) {
 #pragma unroll
                         for (int ii = 0; ii < 4; ii++)
 #pragma unroll
@@ -377,9 +420,9 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
                         const float gv = gp[4 * h + ii];
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            const float term = gv * copysignf(ex2_approx(p.pm1 * lg[ii][k]), u[ii][k]);
-                            gx[4 * h + ii][k] += term;
-                            gwp[k] += term;
+                            const float ps = copysignf(ex2_approx(p.pm1 * lg[ii][k]), u[ii][k]);
+                            gx[4 * h + ii][k] = fmaf(gv, ps, gx[4 * h + ii][k]);
+                            gwp[k] = fmaf(gv, ps, gwp[k]);
                         }
                     }
                 }
@@ -401,78 +444,83 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const LpBwdParams p) {
             }
         }
     }
+    const bool whole = t_begin == 0 && t_end == ntiles;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int b = b0 + tb * 8 + i;
         if (b >= p.B) continue;
 #pragma unroll
-        for (int k = 0; k < 4; k++)
-            if (col[k] >= 0) p.gx[(size_t)b * p.CI + c0 + k] = gx[i][k];
+        for (int k = 0; k < 4; k++) {
+            if (col[k] < 0) continue;
+            float* dst = p.gx + (size_t)b * p.CI + c0 + k;
+            if (whole) *dst = gx[i][k];
+            else atomicAdd(dst, gx[i][k]);
+        }
     }
+    u += t_end - t_begin;
+  }
 }
 
-template <int IP, int NT>
-struct LpBwdLaunch {
-    static constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * 33) * (int)sizeof(float);
-    static int ctas_per_sm(cudaError_t* err) {
-        static int cached[64] = {};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        int& cps = cached[dev & 63];
-        if (cps == 0) {
-            auto kern = lp_bwd_kernel<IP, NT>;
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-            int occ = 0;
-            if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
-            if (e != cudaSuccess) {
-                *err = e;
-                return 0;
-            }
-            cps = occ > 0 ? occ : 1;
-        }
-        return cps;
-    }
-    static double cost(const LpBwdParams& q, cudaError_t* err) {
-        const int cps = ctas_per_sm(err);
-        if (cps == 0) return 1e300;
-        const long long ctas = (long long)((q.B + 31) / 32) * ((q.CI + NT - 1) / NT);
-        const long long slots = (long long)sm_count() * cps;
-        return (double)((ctas + slots - 1) / slots) * cps * NT;
-    }
-    static cudaError_t launch(const LpBwdParams& q, cudaStream_t st) {
-        cudaError_t err = cudaSuccess;
-        if (ctas_per_sm(&err) == 0) return err;
-        dim3 grid((q.B + 31) / 32, (q.CI + NT - 1) / NT);
-        lp_bwd_kernel<IP, NT><<<grid, NT, SMEM, st>>>(q);
-        return cudaGetLastError();
-    }
-};
-
-// Column-tile width (= threads per CTA) with the fewest waves x work per wave.
+// One CTA per resident slot (SMs x CTAs per SM by the occupancy calculator), each with an equal
+// share of the work units; grad_x is zero-filled first because partial ranges add into it.
 template <int IP>
 static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
-    cudaError_t err = cudaSuccess;
-    const double c256 = LpBwdLaunch<IP, 256>::cost(q, &err);
-    const double c128 = LpBwdLaunch<IP, 128>::cost(q, &err);
-    if (err != cudaSuccess) return err;
-    return c256 <= c128 ? LpBwdLaunch<IP, 256>::launch(q, st) : LpBwdLaunch<IP, 128>::launch(q, st);
+    constexpr int NT = 128;
+    constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * 33) * (int)sizeof(float);
+    static int cached[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int& cps = cached[dev & 63];
+    auto kern = lp_bwd_kernel<IP, NT>;
+    if (cps == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        int occ = 0;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
+        if (e != cudaSuccess) return e;
+        cps = occ > 0 ? occ : 1;
+    }
+    const long long total = (long long)((q.B + 31) / 32) * ((q.CI + NT - 1) / NT) * ((q.CO + LPB_JT - 1) / LPB_JT);
+    const long long slots = (long long)sm_count() * cps;
+    cudaError_t e = cudaMemsetAsync(q.gx, 0, sizeof(float) * (size_t)q.B * q.CI, st);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)(total < slots ? total : slots), NT, SMEM, st>>>(q);
+    return cudaGetLastError();
 }
 
+// p.m == nullptr with NORM: the maxima are in y and no scratch is available -> one CTA per tile,
+// finished in the kernel.  Otherwise equal (tile, k-tile) ranges over all resident CTA slots.
 template <int WN, int MODE, int IP, bool NORM>
-static cudaError_t launch_lp_fwd(const LpFwdParams& p, cudaStream_t st) {
+static cudaError_t launch_lp_fwd(LpFwdParams p, cudaStream_t st) {
     constexpr int BN = 64 * WN;
     constexpr int SMEM = 2 * (32 + BN) * LDS * (int)sizeof(float);
     auto kern = lp_fwd_kernel<WN, MODE, IP, NORM>;
-    static bool configured[64] = {};
+    static int cached[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    int& cps = cached[dev & 63];
+    if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        int occ = 0;
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WN * 32, SMEM);
         if (e != cudaSuccess) return e;
-        configured[dev & 63] = true;
+        cps = occ > 0 ? occ : 1;
     }
-    dim3 grid((p.B + 31) / 32, (p.CO + BN - 1) / BN);
-    kern<<<grid, WN * 32, SMEM, st>>>(p);
+    const long long tiles = (long long)((p.B + 31) / 32) * ((p.CO + BN - 1) / BN);
+    const long long slots = (long long)sm_count() * cps;
+    const bool no_scratch = NORM && p.m == nullptr;
+    // whole tiles per CTA when they fill the slots evenly anyway, or when there is nowhere to keep M
+    p.direct = (no_scratch || tiles % slots == 0) ? 1 : 0;
+    if (NORM && p.m == nullptr) p.m = p.y;
+    if (p.direct) {
+        kern<<<(unsigned)tiles, WN * 32, SMEM, st>>>(p);
+        return cudaGetLastError();
+    }
+    const size_t n = (size_t)p.B * p.CO;
+    cudaError_t e = cudaMemsetAsync(p.y, 0, sizeof(float) * n, st);
+    if (e != cudaSuccess) return e;
+    const long long units = tiles * ((p.CI + BK - 1) / BK);
+    kern<<<(unsigned)(units < slots ? units : slots), WN * 32, SMEM, st>>>(p);
+    lp_finish_kernel<<<sm_count() * 4, 256, 0, st>>>(p.y, NORM ? p.m : nullptr, (long long)n, 1.0f / p.p);
     return cudaGetLastError();
 }
 
@@ -492,23 +540,25 @@ static int integer_power(float p) {
 
 using namespace snb;
 
-extern "C" int snb_norm_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G,
-                                     int HW, float* y, float p, const int* w_index_ci,
-                                     const int* w_index_co, int W_CO, int W_CI, void* stream) {
+static int lp_forward_impl(const float* x, const float* w, int B, int CO, int CI, int G, int HW, float* y,
+                           float p, const int* w_index_ci, const int* w_index_co, int W_CO, int W_CI,
+                           float* scratch, cudaStream_t st) {
     if (!(p > 0) || isinf(p)) return SNB_ERR_UNSUPPORTED;
     if (G != 1 || HW != 1)
-        return general_lp_forward(x, w, B, CO, CI, G, HW, y, p, w_index_ci, w_index_co, W_CO, W_CI,
-                                  (cudaStream_t)stream);
+        return general_lp_forward(x, w, B, CO, CI, G, HW, y, p, w_index_ci, w_index_co, W_CO, W_CI, st);
     if (!x || !w || !y) return SNB_ERR_NULL_POINTER;
     if (B <= 0 || CO <= 0 || CI <= 0 || W_CO <= 0 || W_CI <= 0) return SNB_ERR_BAD_SHAPE;
     if ((!w_index_ci && W_CI != CI) || (!w_index_co && W_CO != CO) || CI > W_CI || CO > W_CO)
         return SNB_ERR_BAD_SHAPE;
     if ((long long)W_CO * W_CI >= (1ll << 31) || (long long)B * CO >= (1ll << 31) || (long long)B * CI >= (1ll << 31))
         return SNB_ERR_TOO_LARGE;
-    cudaStream_t st = (cudaStream_t)stream;
-    LpFwdParams q{x, w, y, w_index_ci, w_index_co, B, CO, CI, W_CI, p};
+    LpFwdParams q{x, w, y, nullptr, w_index_ci, w_index_co, B, CO, CI, W_CI, p, 0};
     if (p > 10.0f) {
-        SNB_CUDA(inf_forward_values(x, w, y, w_index_ci, w_index_co, B, CO, CI, W_CI, st));
+        // the maxima go to the scratch array when there is one (y is then free to collect partial
+        // sums from CTAs that share a tile), else into y itself
+        float* maxima = scratch ? scratch : y;
+        SNB_CUDA(inf_forward_values(x, w, maxima, w_index_ci, w_index_co, B, CO, CI, W_CI, st));
+        q.m = scratch;
         SNB_CUDA(dispatch_lp_mode<-1, true>(q, st));
         return SNB_OK;
     }
@@ -524,6 +574,30 @@ extern "C" int snb_norm_dist_forward(const float* x, const float* w, int B, int 
         default: SNB_CUDA(dispatch_lp_mode<-1, false>(q, st)); break;
     }
     return SNB_OK;
+}
+
+extern "C" int snb_norm_dist_forward(const float* x, const float* w, int B, int CO, int CI, int G,
+                                     int HW, float* y, float p, const int* w_index_ci,
+                                     const int* w_index_co, int W_CO, int W_CI, void* stream) {
+    return lp_forward_impl(x, w, B, CO, CI, G, HW, y, p, w_index_ci, w_index_co, W_CO, W_CI, nullptr,
+                           (cudaStream_t)stream);
+}
+
+extern "C" size_t snb_norm_dist_forward_workspace_bytes(int B, int CO, float p) {
+    return (B > 0 && CO > 0 && p > 10.0f) ? sizeof(float) * (size_t)B * (size_t)CO : 0;
+}
+
+extern "C" int snb_norm_dist_forward_ws(const float* x, const float* w, int B, int CO, int CI, int G,
+                                        int HW, float* y, float p, const int* w_index_ci,
+                                        const int* w_index_co, int W_CO, int W_CI, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+    float* scratch = nullptr;
+    if (workspace && p > 10.0f) {
+        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return SNB_ERR_ALIGNMENT;
+        if (workspace_bytes >= snb_norm_dist_forward_workspace_bytes(B, CO, p)) scratch = (float*)workspace;
+    }
+    return lp_forward_impl(x, w, B, CO, CI, G, HW, y, p, w_index_ci, w_index_co, W_CO, W_CI, scratch,
+                           (cudaStream_t)stream);
 }
 
 static int lp_backward(const float* g, const float* x, const float* w, const float* y, int B, int CO,

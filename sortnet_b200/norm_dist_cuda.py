@@ -49,7 +49,7 @@ def _dims(x, out):
 # Kernels launched by each C entry point (memsets are not counted).
 _KERNELS = {
     "snb_inf_dist_forward": 2, "snb_inf_dist_forward_ws": 2, "snb_inf_dist_forward_nograd": 1, "snb_inf_dist_backward_input": 1,
-    "snb_inf_dist_backward_input_weight": 1, "snb_norm_dist_forward": 1, "snb_norm_dist_backward_input": 1,
+    "snb_inf_dist_backward_input_weight": 1, "snb_norm_dist_forward": 1, "snb_norm_dist_forward_ws": 2, "snb_norm_dist_backward_input": 1,
     "snb_norm_dist_backward_input_weight": 1, "snb_bound_inf_dist_forward_nograd": 1,
     "snb_bound_inf_dist_forward": 1, "snb_bound_inf_dist_backward_input": 1,
     "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1,
@@ -99,7 +99,7 @@ def _call(dev, ref_tensor, entry, tag, *args):
             _timeline.append((entry, tag, e0, e1))
     _lib.check(rc, entry[4:])
     launch_count += _KERNELS[entry]
-    if entry == "snb_norm_dist_forward" and args[8] > 10.0:
+    if entry in ("snb_norm_dist_forward", "snb_norm_dist_forward_ws") and args[8] > 10.0:
         launch_count += 1      # the l-inf pass that supplies the normaliser
 
 
@@ -182,9 +182,13 @@ def norm_dist_forward(input, weight, output, G, p, w_index_ci=None, w_index_co=N
     _check(input, "input"); _check(weight, "weight"); _check(output, "output")
     B, CO, CI, HW = _lp_common(input, weight, output, w_index_ci, w_index_co, G)
     dev = _same_device(input, weight, output, w_index_ci, w_index_co)
-    _call(dev, input, "snb_norm_dist_forward", (B, CO, CI),
+    # p > 10: scratch for the maxima (4 bytes per output) from PyTorch's caching allocator, so that
+    # the kernel may share output tiles between thread blocks
+    ws = torch.empty(B * CO * HW if p > 10 else 0, dtype=torch.float32, device=dev)
+    _call(dev, input, "snb_norm_dist_forward_ws", (B, CO, CI),
           _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), float(p), _ptr(w_index_ci),
-          _ptr(w_index_co), weight.size(0), weight.size(1) * G)
+          _ptr(w_index_co), weight.size(0), weight.size(1) * G, ws.data_ptr() if ws.numel() else None,
+          ws.numel() * 4)
 
 
 def norm_dist_forward_with_max(input, weight, max_output, output, G, p, w_index_ci=None, w_index_co=None):
