@@ -278,14 +278,17 @@ struct LpBwdParams {
 // The gathered W tile [32 j][NT c] and the (g, y) tile of the next j tile are fetched with
 // cp.async while the current one is consumed.
 constexpr int LPB_JT = 32;
+// floats per row of the (g, 1/y) tiles [j][row]: 16-byte aligned rows, so that a thread's eight rows
+// are two vector loads (all lanes of a warp that share tb read the same words: broadcast)
+constexpr int LPB_GLD = 36;
 
 template <int IP, int NT>
 __global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpBwdParams p) {
     constexpr int LPB_WLD = NT + 4;  // floats per W-tile row (+4: keeps 16-byte alignment, shifts banks)
     extern __shared__ __align__(16) float smem[];
     float* wt = smem;                                   // [2][JT][WLD]
-    float* gt = smem + 2 * LPB_JT * LPB_WLD;            // [2][JT][33]  g
-    float* yt = gt + 2 * LPB_JT * 33;                   // [2][JT][33]  y, turned into 1/y in place
+    float* gt = smem + 2 * LPB_JT * LPB_WLD;            // [2][JT][GLD]  g
+    float* yt = gt + 2 * LPB_JT * LPB_GLD;                   // [2][JT][GLD]  y, turned into 1/y in place
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tb = lane & 3, tc = warp * 8 + (lane >> 2);
     const int ntiles = (p.CO + LPB_JT - 1) / LPB_JT;
@@ -341,8 +344,8 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpB
             const int b = b0 + bb, j = j0 + jj;
             const bool ok = b < p.B && j < p.CO;
             const size_t o = ok ? (size_t)b * p.CO + j : 0;
-            cp_async4(smem_u32(gt + (st * LPB_JT + jj) * 33 + bb), p.g + o, ok ? 4 : 0);
-            cp_async4(smem_u32(yt + (st * LPB_JT + jj) * 33 + bb), p.y + o, ok ? 4 : 0);
+            cp_async4(smem_u32(gt + (st * LPB_JT + jj) * LPB_GLD + bb), p.g + o, ok ? 4 : 0);
+            cp_async4(smem_u32(yt + (st * LPB_JT + jj) * LPB_GLD + bb), p.y + o, ok ? 4 : 0);
         }
     };
 
@@ -358,7 +361,7 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpB
 #pragma unroll
         for (int r = 0; r < 1024 / NT; r++) {  // y -> 1/y (0 for padding), each thread its own elements
             const int e = tid + NT * r;
-            const int o = (st * LPB_JT + (e & 31)) * 33 + (e >> 5);
+            const int o = (st * LPB_JT + (e & 31)) * LPB_GLD + (e >> 5);
             const float v = yt[o];
             const float ry = v > 0.f ? 1.0f / v : 0.f;
             yt[o] = ry;
@@ -373,8 +376,19 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpB
             const float4 wv4 = *reinterpret_cast<const float4*>(wt + (st * LPB_JT + jj) * LPB_WLD + tc * 4);
             const float wv[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
             float gwp[4] = {0.f, 0.f, 0.f, 0.f};
-            const float* gp = gt + (st * LPB_JT + jj) * 33 + tb * 8;
-            const float* yp = yt + (st * LPB_JT + jj) * 33 + tb * 8;
+            float gp[8], yp[8];
+            {
+                const float4* g4 = reinterpret_cast<const float4*>(gt + (st * LPB_JT + jj) * LPB_GLD + tb * 8);
+                const float4* y4 = reinterpret_cast<const float4*>(yt + (st * LPB_JT + jj) * LPB_GLD + tb * 8);
+                const float4 ga = g4[0], gb = g4[1];
+                gp[0] = ga.x; gp[1] = ga.y; gp[2] = ga.z; gp[3] = ga.w;
+                gp[4] = gb.x; gp[5] = gb.y; gp[6] = gb.z; gp[7] = gb.w;
+                if (IP < 0) {
+                    const float4 ya = y4[0], yb = y4[1];
+                    yp[0] = ya.x; yp[1] = ya.y; yp[2] = ya.z; yp[3] = ya.w;
+                    yp[4] = yb.x; yp[5] = yb.y; yp[6] = yb.z; yp[7] = yb.w;
+                }
+            }
             if (IP >= 0) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
@@ -466,7 +480,7 @@ __global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpB
 template <int IP>
 static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
     constexpr int NT = 128;
-    constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * 33) * (int)sizeof(float);
+    constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * LPB_GLD) * (int)sizeof(float);
     static int cached[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
