@@ -76,6 +76,8 @@ def load(build_if_missing: bool = False):
     lib.snb_inf_dist_forward_noalloc_max_outputs.restype = ctypes.c_int
     lib.snb_inf_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.snb_inf_dist_forward_workspace_bytes.restype = ctypes.c_size_t
+    lib.snb_norm_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_float]
+    lib.snb_norm_dist_forward_workspace_bytes.restype = ctypes.c_size_t
     _lib = lib
     return lib
 

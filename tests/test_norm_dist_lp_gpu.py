@@ -101,3 +101,48 @@ def test_large_p_approaches_inf():
     C.inf_dist_forward_nograd(col3(x), dev(w), y_inf, 1)
     y = run_fwd(x, w, 1000.0)
     assert (y >= host(y_inf) * (1 - 1e-6)).all() and rel(y, host(y_inf)) < 1e-2
+
+
+@pytest.mark.parametrize("p", [8.0, 12.5, 100.0])
+@pytest.mark.parametrize("B,CI,CO,keep", [(70, 150, 300, None), (96, 300, 520, 0.8), (512, 640, 1100, 0.9)])
+def test_entry_point_without_scratch(p, B, CI, CO, keep):
+    """snb_norm_dist_forward (no scratch: one thread block per output tile when p > 10) against the
+    oracle and against snb_norm_dist_forward_ws (thread blocks share tiles, partial sums merge with
+    atomics): both within the tolerance of the exact value, and within 2e-6 of each other."""
+    from sortnet_b200 import _lib
+    rng = np.random.default_rng(int(p) + B)
+    ci = co = None
+    if keep is not None:
+        ci, co = make_masks(rng, B, CI, keep), make_masks(rng, B, CO, keep)
+    ci_n = CI if ci is None else ci.shape[-1]
+    co_n = CO if co is None else co.shape[-1]
+    x = rng.random((B, ci_n), dtype=np.float32)
+    w = rng.standard_normal((CO, CI)).astype(np.float32)
+    y_o = oracle.norm_dist_forward(x, w, p, ci, co)
+    X, W, CI_, CO_ = col3(x), dev(w), idx3(ci), idx3(co)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    y_plain = torch.full((B, co_n, 1), float("nan"), device="cuda")
+    rc = lib.snb_norm_dist_forward(X.data_ptr(), W.data_ptr(), B, co_n, ci_n, 1, 1, y_plain.data_ptr(), p,
+                                   ptr(CI_), ptr(CO_), CO, CI, stream)
+    assert rc == 0
+    n_ws = lib.snb_norm_dist_forward_workspace_bytes(B, co_n, p)
+    assert n_ws == (4 * B * co_n if p > 10 else 0)
+    ws = torch.empty(max(n_ws, 16) // 4, device="cuda")
+    y_ws = torch.full((B, co_n, 1), float("nan"), device="cuda")
+    rc = lib.snb_norm_dist_forward_ws(X.data_ptr(), W.data_ptr(), B, co_n, ci_n, 1, 1, y_ws.data_ptr(), p,
+                                      ptr(CI_), ptr(CO_), CO, CI, ws.data_ptr(), n_ws, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert rel(host(y_plain), y_o) < TOL and rel(host(y_ws), y_o) < TOL
+    assert rel(host(y_plain), host(y_ws)) < 2e-6
+    # a misaligned scratch pointer is refused, a short one falls back to the scratch-free kernel
+    if p > 10:
+        assert lib.snb_norm_dist_forward_ws(X.data_ptr(), W.data_ptr(), B, co_n, ci_n, 1, 1, y_ws.data_ptr(), p,
+                                            ptr(CI_), ptr(CO_), CO, CI, ws.data_ptr() + 4, n_ws, stream) == 6
+        y_short = torch.full((B, co_n, 1), float("nan"), device="cuda")
+        assert lib.snb_norm_dist_forward_ws(X.data_ptr(), W.data_ptr(), B, co_n, ci_n, 1, 1, y_short.data_ptr(), p,
+                                            ptr(CI_), ptr(CO_), CO, CI, ws.data_ptr(), n_ws - 4, stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(y_short, y_plain)
