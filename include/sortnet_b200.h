@@ -237,6 +237,16 @@ int snb_mean_shift_stats(const float* x, const int* index, int B, int C, int C_f
 int snb_mean_shift_apply(const float* x, const float* mean, const int* index, int B, int C,
                          float* y, void* stream);
 
+/* ---- mask sampling ---------------------------------------------------------------------------- */
+
+/* out [lists, count] int32: for each list an independent, uniformly random subset of
+ * {0 .. channels-1} with exactly `count` elements, ascending.  Deterministic in (seed, lists,
+ * channels, count).  channels <= 51200.  Replaces sample_mask (core/models/norm_dist.py:14-17:
+ * uniform scores + top-k in PyTorch; the reference leaves the lists unsorted, the order carries no
+ * meaning); the caller draws `count` ~ Binomial(channels, keep rate) itself because it fixes the
+ * tensor shapes. */
+int snb_sample_mask(int* out, int lists, int channels, int count, unsigned long long seed, void* stream);
+
 /* ---- optimiser ------------------------------------------------------------------------------- */
 
 /* One AdamW step over flat buffers of n fp32 values (n a multiple of 4, 16-byte aligned), with the

@@ -32,7 +32,20 @@ SUB_BATCH = 32
 def sample_mask(batch, groups, channel, q, device, count=None):
     """Kept-channel lists for `batch` sub-batches: one Binomial(channel, q) count shared by all
     sub-batches (drawn here unless the caller supplies it), a uniformly random subset of that
-    size per (sub-batch, group), sorted, int32, shape [batch, groups, count]."""
+    size per (sub-batch, group), sorted, int32, shape [batch, groups, count].
+
+    On a CUDA device the count and a 64-bit seed come from PyTorch's host generator (so
+    torch.manual_seed makes the masks reproducible and nothing waits for the GPU) and one kernel
+    writes all lists; on the CPU the lists are made with PyTorch ops the way the reference does."""
+    device = torch.device(device)
+    if device.type == "cuda":
+        if count is None:
+            count = int((torch.rand(channel) < q).sum())
+        count = min(max(int(count), 1), channel)
+        seed = int(torch.randint(0, 2 ** 62, (1,)))
+        out = torch.empty(batch, groups, count, dtype=torch.int32, device=device)
+        _C.sample_mask_into(out, channel, seed)
+        return out
     if count is None:
         count = int((torch.rand(channel, device=device) < q).sum().item())
     scores = torch.rand(batch, groups, channel, device=device)
@@ -354,14 +367,11 @@ class SortMLPModel(nn.Module):
         masks = [None] * (len(self.fc_dist) - 1)
         if not todo:
             return masks
-        # all Binomial counts in one device round trip (one host synchronisation per step
-        # instead of one per layer)
-        width = max(l.in_features for _, l in todo)
-        u = torch.rand(len(todo), width, device=device)
-        keep = torch.tensor([l.keep_rate for _, l in todo], device=device).unsqueeze(1)
-        valid = torch.arange(width, device=device).unsqueeze(0) < torch.tensor(
-            [l.in_features for _, l in todo], device=device).unsqueeze(1)
-        counts = ((u < keep) & valid).sum(dim=1).tolist()
+        # The Binomial(in_features, keep) counts fix tensor shapes, so the host must know them: they
+        # are drawn from the host generator (a few thousand uniforms) instead of on the device, which
+        # would cost a device synchronisation per step and stop the host from queueing kernels
+        # ahead of the GPU.
+        counts = [int((torch.rand(l.in_features) < l.keep_rate).sum()) for _, l in todo]
         for (k, l), c in zip(todo, counts):
             masks[k] = sample_mask(sub, 1, l.in_features, l.keep_rate, device, count=max(int(c), 1))
         return masks

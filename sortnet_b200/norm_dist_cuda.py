@@ -52,7 +52,7 @@ _KERNELS = {
     "snb_inf_dist_backward_input_weight": 1, "snb_norm_dist_forward": 1, "snb_norm_dist_forward_ws": 2, "snb_norm_dist_backward_input": 1,
     "snb_norm_dist_backward_input_weight": 1, "snb_bound_inf_dist_forward_nograd": 1,
     "snb_bound_inf_dist_forward": 1, "snb_bound_inf_dist_backward_input": 1,
-    "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1,
+    "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1, "snb_sample_mask": 1,
     "snb_sort_neuron_forward_nograd": 1, "snb_sort_neuron_forward": 1, "snb_bound_sort_neuron_forward": 1,
     "snb_sort_neuron_backward_input": 1, "snb_sort_neuron_backward_input_weight": 1,
 }
@@ -377,6 +377,16 @@ def mean_shift_apply(x, mean, index, y):
     dev = _same_device(x, mean, index, y)
     _call(dev, x, "snb_mean_shift_apply", (B, C),
           _ptr(x), _ptr(mean), _ptr(index), B, C, _ptr(y))
+
+
+def sample_mask_into(out, channels, seed):
+    """out [S, G, count] int32 CUDA tensor -> S * G independent sorted subsets of range(channels)."""
+    _check(out, "out", torch.int32)
+    if out.dim() != 3:
+        raise RuntimeError("out must have shape [sub-batches, groups, count]")
+    lists, count = out.size(0) * out.size(1), out.size(2)
+    _call(out.device, out, "snb_sample_mask", (lists, channels, count),
+          _ptr(out), lists, int(channels), count, int(seed) & 0xFFFFFFFFFFFFFFFF)
 
 
 def install():

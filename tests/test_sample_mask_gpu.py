@@ -1,0 +1,90 @@
+"""The mask sampler kernel: format (sorted, distinct, exact count), reproducibility, uniformity, and
+bit-exact agreement with a numpy restatement of its algorithm (Philox-4x32-10 keys, keep the
+`count` smallest, ties in channel order)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+M0, M1, W0, W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
+
+
+def philox_keys(lists, channels, seed):
+    """keys[list, channel] as the kernel draws them: counter (channel // 4, list, 0, 0), key = seed."""
+    q = np.arange((channels + 3) // 4, dtype=np.uint64)
+    c = [np.broadcast_to(q, (lists, q.size)).copy(),
+         np.broadcast_to(np.arange(lists, dtype=np.uint64)[:, None], (lists, q.size)).copy(),
+         np.zeros((lists, q.size), np.uint64), np.zeros((lists, q.size), np.uint64)]
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64((seed >> 32) & 0xFFFFFFFF)
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(M0) * c[0]
+        p1 = np.uint64(M1) * c[2]
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0 = (k0 + np.uint64(W0)) & mask
+        k1 = (k1 + np.uint64(W1)) & mask
+    keys = np.stack(c, axis=-1).reshape(lists, -1)[:, :channels]
+    return keys.astype(np.uint32)
+
+
+def expected_lists(lists, channels, count, seed):
+    keys = philox_keys(lists, channels, seed)
+    order = np.argsort(keys, axis=1, kind="stable")        # ties: lower channel first
+    return np.sort(order[:, :count], axis=1).astype(np.int32)
+
+
+def draw(S, G, channels, count, seed):
+    from sortnet_b200 import norm_dist_cuda as C
+    out = torch.full((S, G, count), -1, dtype=torch.int32, device="cuda")
+    C.sample_mask_into(out, channels, seed)
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("S,G,channels,count", [(16, 1, 5120, 4608), (3, 2, 50, 40), (4, 1, 12288, 11000),
+                                                (2, 3, 37, 1), (5, 1, 1023, 1023), (1, 1, 7, 3)])
+def test_matches_the_restated_algorithm(S, G, channels, count):
+    seed = 0x1234567890ABCDEF + channels
+    got = draw(S, G, channels, count, seed)
+    assert np.array_equal(got.reshape(S * G, count), expected_lists(S * G, channels, count, seed))
+    assert (np.diff(got, axis=-1) > 0).all() and got.min() >= 0 and got.max() < channels
+    again = draw(S, G, channels, count, seed)
+    assert np.array_equal(got, again)
+    if count < channels:
+        assert not np.array_equal(got, draw(S, G, channels, count, seed + 1))
+
+
+def test_uniform_over_channels():
+    lists, channels, count = 4096, 96, 24
+    got = draw(lists, 1, channels, count, 99).reshape(lists, count)
+    freq = np.bincount(got.ravel(), minlength=channels) / lists
+    sigma = np.sqrt(0.25 * 0.75 / lists)
+    assert np.abs(freq - 0.25).max() < 5 * sigma
+    # channels 0 and 1 are kept together about count*(count-1)/(channels*(channels-1)) of the time
+    both = (np.isin(0, got[:, :1]) if False else ((got == 0).any(1) & (got == 1).any(1))).mean()
+    want = count * (count - 1) / (channels * (channels - 1))
+    assert abs(both - want) < 5 * np.sqrt(want * (1 - want) / lists)
+
+
+def test_layer_level_sampler_is_reproducible_and_sorted():
+    from sortnet_b200.layers import sample_mask
+    torch.manual_seed(5)
+    a = sample_mask(4, 2, 300, 0.8, "cuda")
+    torch.manual_seed(5)
+    b = sample_mask(4, 2, 300, 0.8, "cuda")
+    assert a.dtype == torch.int32 and a.dim() == 3 and a.shape[:2] == (4, 2)
+    assert torch.equal(a, b)
+    assert bool((a[..., 1:] > a[..., :-1]).all()) and int(a.min()) >= 0 and int(a.max()) < 300
+    assert abs(a.size(-1) - 240) < 40
+    c = sample_mask(4, 2, 300, 0.8, "cuda", count=17)
+    assert c.shape == (4, 2, 17)
+
+
+def test_bad_arguments():
+    from sortnet_b200 import norm_dist_cuda as C
+    out = torch.empty(2, 1, 10, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError):
+        C.sample_mask_into(out, 5, 1)              # more elements than channels
+    with pytest.raises(RuntimeError):
+        C.sample_mask_into(out.float(), 50, 1)     # wrong dtype
