@@ -40,12 +40,14 @@ __device__ __forceinline__ float combine(const float (&res)[KMAX], int K, float 
     return ans / (1 - c);
 }
 
-// CTA of 256 threads, TM x TN outputs per thread (rows ty + 16 i, columns tx + 16 j): 4 x 4 for
-// up to 10 slots, 2 x 4 for up to 25; BOUND carries two chains per output (bottom-K of
-// min(t1,t2), top-K of max(t1,t2)) on TM x 2 outputs.
+// CTA of 256 threads, TM x TN outputs per thread (rows ty + 16 i, columns tx + 16 j): 2 x 2 for up to
+// 10 slots (64 registers for values, 128 for bounds: 4 resp. 2 CTAs per SM - the kernel lives on
+// hiding the subtract -> compare -> vote -> branch latency of every element, so resident warps
+// matter more than operand reuse), 2 x 4 resp. 2 x 2 for up to 25 slots; BOUND carries two chains
+// per output (bottom-K of min(t1,t2), top-K of max(t1,t2)).
 template <int KMAX, bool BOUND>
-__global__ void __launch_bounds__(256) sort_fwd_kernel(const SortParams p) {
-    constexpr int TM = KMAX > 10 ? 2 : 4, TN = BOUND ? 2 : 4, BM = 16 * TM, BN = 16 * TN, NT = 256;
+__global__ void __launch_bounds__(256, KMAX > 10 ? 1 : (BOUND ? 2 : 4)) sort_fwd_kernel(const SortParams p) {
+    constexpr int TM = 2, TN = (BOUND || KMAX <= 10) ? 2 : 4, BM = 16 * TM, BN = 16 * TN, NT = 256;
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;                              // [2][BM][LDS]
     float* us = xs + 2 * BM * LDS;                 // [2][BM][LDS] (BOUND)
@@ -255,7 +257,7 @@ __global__ void __launch_bounds__(256) sort_bwd_kernel(const float* __restrict__
 
 template <int KMAX, bool BOUND>
 static cudaError_t launch_sort_fwd(const SortParams& p, cudaStream_t st) {
-    constexpr int BM = KMAX > 10 ? 32 : 64, BN = BOUND ? 32 : 64;
+    constexpr int BM = 32, BN = (BOUND || KMAX <= 10) ? 32 : 64;
     constexpr int SMEM = 2 * ((BOUND ? 2 : 1) * BM + BN) * LDS * (int)sizeof(float);
     auto kern = sort_fwd_kernel<KMAX, BOUND>;
     static bool configured[64] = {};
