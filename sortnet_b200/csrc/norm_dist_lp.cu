@@ -283,7 +283,7 @@ constexpr int LPB_JT = 32;
 constexpr int LPB_GLD = 36;
 
 template <int IP, int NT>
-__global__ void __launch_bounds__(NT, NT == 128 ? 3 : 1) lp_bwd_kernel(const LpBwdParams p) {
+__global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdParams p) {
     constexpr int LPB_WLD = NT + 4;  // floats per W-tile row (+4: keeps 16-byte alignment, shifts banks)
     extern __shared__ __align__(16) float smem[];
     float* wt = smem;                                   // [2][JT][WLD]
