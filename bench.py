@@ -181,6 +181,9 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # stdout carries the one JSON line: NCCL's own log lines (its version banner, anything
+        # NCCL_DEBUG asks for) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         # SNB_NCCL_MAX_CTAS > 0 caps the CTAs NCCL may use.  Measured at N = 8: 2 / 4 / 8 CTAs give
         # 31.1 / 29.3 / 28.5 ms per step, NCCL's own choice 27.2 ms, so the default is no cap.
         opts = dist.ProcessGroupNCCL.Options()
@@ -200,15 +203,20 @@ def run_gpu_arm(args):
     torch.manual_seed(1 + rank)  # masks and data differ per rank, like the reference's seed + rank
     # parameters, gradients and AdamW moments in flat buffers: one all-reduce, one fused update,
     # weight gradients written in place by the backward kernels
-    # N > 1: gradient exchange and optimiser are one kernel over NVLink peer memory
-    # (SNB_PEER_STEP=0 falls back to one NCCL all-reduce followed by the local fused AdamW)
+    # N > 1: the gradient exchange runs as device-to-device copies over NVLink on a side stream,
+    # beside the bound pass, with a local sum + AdamW kernel for this rank's shard in between
+    # (SNB_COPY_EXCHANGE=0: one fused kernel over peer memory, not overlapped; SNB_PEER_STEP=0: one
+    # NCCL all-reduce followed by the local fused AdamW)
     peer_step = world > 1 and os.environ.get("SNB_PEER_STEP", "1") != "0"
     adam = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
     exchange = "none (single GPU)"
     if peer_step:
         try:
-            opt = FlatAdamW(model, peer_memory=True, **adam)
-            exchange = "fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory"
+            copy_exchange = os.environ.get("SNB_COPY_EXCHANGE", "1") != "0"
+            opt = FlatAdamW(model, peer_memory=True, overlap=copy_exchange, **adam)
+            exchange = ("device-to-device copies over NVLink (reduce-scatter, all-gather) + local sum/AdamW kernel, "
+                        "all beside the bound pass" if copy_exchange else
+                        "fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory")
         except Exception as exc:                          # symmetric memory not available: use NCCL
             if rank == 0:
                 print("peer-memory step unavailable (%s); using one NCCL all-reduce" % exc, file=sys.stderr)
@@ -243,7 +251,12 @@ def run_gpu_arm(args):
         opt.zero_grad()
         loss.backward()
         opt.gather_grads()
-        if overlap_bounds:
+        if opt.overlap:
+            opt.begin_exchange()                          # side stream: copies + the shard's update
+            with torch.no_grad():
+                cert = model.certified_margin(x, t, eps_b, up, down)   # reads the pre-update weights
+            opt.end_exchange()
+        elif overlap_bounds:
             work = opt.all_reduce(async_op=True)          # certification pass overlaps the exchange
             with torch.no_grad():
                 cert = model.certified_margin(x, t, eps_b, up, down)

@@ -256,6 +256,17 @@ int snb_sample_mask(int* out, int lists, int channels, int count, unsigned long 
 int snb_adamw_step(float* w, const float* g, float* m, float* v, long long n, float lr, float beta1,
                    float beta2, float eps, float weight_decay, int step, float grad_scale, void* stream);
 
+/* snb_adamw_step with the gradient given as `parts` (<= 16) partial buffers of n values each (a host
+ * array of device pointers; summed in index order, then multiplied by grad_scale) and the new values
+ * written to w_dst (may equal w_src).  It is the local part of a data-parallel step whose
+ * reduce-scatter and all-gather are device-to-device copies that run beside other kernels; the
+ * two parameter buffers let those kernels keep reading the old values meanwhile.
+ * Replaces DistributedDataParallel's all-reduce plus optimizer.step() (main.py:402,95) together
+ * with the copies. */
+int snb_adamw_reduce_step(const float* w_src, float* w_dst, const void* const* grad_parts, int parts, float* m,
+                          float* v, long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                          int step, float grad_scale, void* stream);
+
 /* Data-parallel AdamW step fused with the gradient exchange: this rank sums elements [lo, hi) of
  * the flat gradient buffers of all `world` ranks (peer pointers of one NVLink node, entry `rank`
  * its own), divides by world, applies AdamW with its shard-sized moments m, v and stores the new

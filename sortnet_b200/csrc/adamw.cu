@@ -39,9 +39,74 @@ __global__ void __launch_bounds__(256) adamw_kernel(float4* __restrict__ w, cons
     }
 }
 
+constexpr int ADAMW_MAX_PARTS = 16;
+struct GradParts {
+    const float4* g[ADAMW_MAX_PARTS];
+};
+
+// The same update with the gradient given as `parts` partial buffers (summed in index order) and
+// the new values written to a second parameter buffer: the local half of a data-parallel step
+// whose reduce-scatter and all-gather are plain device-to-device copies.
+__global__ void __launch_bounds__(256) adamw_reduce_kernel(const float4* __restrict__ w_src, float4* __restrict__ w_dst,
+                                                           const GradParts parts, int n_parts, float4* __restrict__ m,
+                                                           float4* __restrict__ v, size_t n4, float decay, float b1,
+                                                           float b2, float step_size, float inv_sqrt_bc2, float eps,
+                                                           float grad_scale) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 gv = parts.g[0][i];
+        for (int r = 1; r < n_parts; r++) {
+            const float4 t = parts.g[r][i];
+            gv.x += t.x;
+            gv.y += t.y;
+            gv.z += t.z;
+            gv.w += t.w;
+        }
+        float4 wv = w_src[i], mv = m[i], vv = v[i];
+        float* wp = reinterpret_cast<float*>(&wv);
+        const float* gp = reinterpret_cast<const float*>(&gv);
+        float* mp = reinterpret_cast<float*>(&mv);
+        float* vp = reinterpret_cast<float*>(&vv);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float gk = gp[k] * grad_scale;
+            mp[k] = b1 * mp[k] + (1.0f - b1) * gk;
+            vp[k] = b2 * vp[k] + (1.0f - b2) * gk * gk;
+            const float denom = sqrtf(vp[k]) * inv_sqrt_bc2 + eps;
+            wp[k] = wp[k] * decay - step_size * (mp[k] / denom);
+        }
+        w_dst[i] = wv;
+        m[i] = mv;
+        v[i] = vv;
+    }
+}
+
 }  // namespace snb
 
 using namespace snb;
+
+extern "C" int snb_adamw_reduce_step(const float* w_src, float* w_dst, const void* const* grad_parts, int parts,
+                                     float* m, float* v, long long n, float lr, float beta1, float beta2, float eps,
+                                     float weight_decay, int step, float grad_scale, void* stream) {
+    if (!w_src || !w_dst || !grad_parts || !m || !v) return SNB_ERR_NULL_POINTER;
+    if (parts < 1 || parts > ADAMW_MAX_PARTS) return SNB_ERR_UNSUPPORTED;
+    if (n <= 0 || step <= 0 || (n & 3)) return SNB_ERR_BAD_SHAPE;
+    if (!aligned16(w_src) || !aligned16(w_dst) || !aligned16(m) || !aligned16(v)) return SNB_ERR_ALIGNMENT;
+    GradParts gp{};
+    for (int r = 0; r < parts; r++) {
+        if (!grad_parts[r]) return SNB_ERR_NULL_POINTER;
+        if (!aligned16(grad_parts[r])) return SNB_ERR_ALIGNMENT;
+        gp.g[r] = reinterpret_cast<const float4*>(grad_parts[r]);
+    }
+    const double bc1 = 1.0 - pow((double)beta1, step), bc2 = 1.0 - pow((double)beta2, step);
+    const float step_size = (float)(lr / bc1), inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
+    adamw_reduce_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const float4*>(w_src), reinterpret_cast<float4*>(w_dst), gp, parts,
+        reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v), (size_t)n / 4, 1.0f - lr * weight_decay, beta1,
+        beta2, step_size, inv_sqrt_bc2, eps, grad_scale);
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}
 
 extern "C" int snb_adamw_step(float* w, const float* g, float* m, float* v, long long n, float lr, float beta1,
                               float beta2, float eps, float weight_decay, int step, float grad_scale,

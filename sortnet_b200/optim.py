@@ -42,11 +42,18 @@ class FlatAdamW:
     """
 
     def __init__(self, module, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, process_group=None,
-                 peer_memory=False):
+                 peer_memory=False, overlap=False):
         """peer_memory=True (ranks of one NVLink node): the flat gradient and parameter buffers are
         allocated as symmetric memory and `step()` runs the fused reduce-scatter + AdamW +
         all-gather kernel over peer pointers instead of an NCCL all-reduce plus a local update;
-        each rank then keeps AdamW moments for its 1/world shard only."""
+        each rank then keeps AdamW moments for its 1/world shard only.
+
+        overlap=True (with peer_memory): the exchange runs beside other work of the step.
+        `begin_exchange()` queues, on a side stream, device-to-device copies of this rank's shard of
+        every peer's gradients (copy engines over NVLink, no SM time), the local sum + AdamW kernel
+        and copies of the updated shard into every peer's *second* parameter buffer;
+        `end_exchange()` makes the main stream wait for them and switches the parameters to that
+        buffer.  Kernels launched in between (the interval-bound pass) keep reading the old values."""
         self.params = [p for p in module.parameters() if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")
@@ -78,13 +85,18 @@ class FlatAdamW:
             self._param_ptrs = arr(*[int(q) for q in self._hdl_param.buffer_ptrs])
             self.lo, self.hi = shard_bounds(total, self.world, self.rank)
             moments = max(self.hi - self.lo, 4)
+            self.overlap = bool(overlap)
+            if self.overlap:
+                self._setup_overlap(symm_mem, group, total, dev)
         else:
             self.flat_param = torch.zeros(total, device=dev, dtype=torch.float32)
             self.flat_grad = torch.zeros(total, device=dev, dtype=torch.float32)
             moments = total
+            self.overlap = False
         self.exp_avg = torch.zeros(moments, device=dev, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(moments, device=dev, dtype=torch.float32)
         self._slices = []
+        self._views = [[], []]          # parameter views into the two parameter buffers (overlap)
         for p, off in zip(self.params, offsets):
             view = self.flat_param[off:off + p.numel()].view_as(p)
             view.copy_(p.data)
@@ -92,6 +104,77 @@ class FlatAdamW:
             sink = self.flat_grad[off:off + p.numel()].view_as(p)
             p.grad_sink = sink
             self._slices.append((p, sink))
+            if self.overlap:
+                self._views[0].append(view)
+                self._views[1].append(self._param_bufs[1][off:off + p.numel()].view_as(p))
+
+    def _setup_overlap(self, symm_mem, group, total, dev):
+        second = symm_mem.empty(total, dtype=torch.float32, device=dev)
+        second.zero_()
+        hdl_second = symm_mem.rendezvous(second, group)
+        self._param_bufs = [self.flat_param, second]
+        self._param_hdls = [self._hdl_param, hdl_second]
+        self._cur = 0
+        n = self.hi - self.lo
+        shape = (max(n, 0),)
+        peers = [r for r in range(self.world) if r != self.rank]
+        # this rank's shard of every peer's gradient buffer / of every peer's parameter buffers
+        self._peer_grad = {r: self._hdl_grad.get_buffer(r, shape, torch.float32, self.lo) for r in peers}
+        self._peer_param = [{r: h.get_buffer(r, shape, torch.float32, self.lo) for r in peers}
+                            for h in self._param_hdls]
+        self._recv = {r: torch.empty(shape, device=dev, dtype=torch.float32) for r in peers}
+        self._side = torch.cuda.Stream(device=dev)
+        self._ready = torch.cuda.Event()
+        self._done = torch.cuda.Event()
+        self._in_flight = False
+
+    def begin_exchange(self):
+        """Queues the gradient exchange and the update of this rank's shard behind everything that
+        is on the current stream now (the backward); returns at once."""
+        if not self.overlap:
+            raise RuntimeError("begin_exchange() needs FlatAdamW(peer_memory=True, overlap=True)")
+        import ctypes
+        self.step_count += 1
+        dev = self.flat_grad.device
+        lo, hi, n = self.lo, self.hi, self.hi - self.lo
+        cur, nxt = self._param_bufs[self._cur], self._param_bufs[self._cur ^ 1]
+        with torch.cuda.device(dev):
+            self._ready.record(torch.cuda.current_stream(dev))
+            self._side.wait_event(self._ready)
+            with torch.cuda.stream(self._side):
+                # every rank's backward has finished writing its gradients ...
+                self._hdl_grad.barrier(channel=0, timeout_ms=60000)
+                rc = 0
+                if n > 0:
+                    for r, src in self._peer_grad.items():
+                        self._recv[r].copy_(src, non_blocking=True)
+                    parts = [self.flat_grad[lo:hi] if r == self.rank else self._recv[r] for r in range(self.world)]
+                    ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in parts])
+                    rc = _lib.load().snb_adamw_reduce_step(
+                        cur[lo:hi].data_ptr(), nxt[lo:hi].data_ptr(), ptrs, self.world, self.exp_avg.data_ptr(),
+                        self.exp_avg_sq.data_ptr(), n, float(self.lr), float(self.betas[0]), float(self.betas[1]),
+                        float(self.eps), float(self.weight_decay), self.step_count, 1.0 / self.world,
+                        self._side.cuda_stream)
+                    for r, dst in self._peer_param[self._cur ^ 1].items():
+                        dst.copy_(nxt[lo:hi], non_blocking=True)
+                # ... and every rank's shard of the new values has landed in this rank's second buffer
+                self._param_hdls[self._cur ^ 1].barrier(channel=0, timeout_ms=60000)
+                self._done.record(self._side)
+        _lib.check(rc, "adamw_reduce_step")
+        _C.launch_count += 1
+        self._in_flight = True
+
+    def end_exchange(self):
+        """The current stream waits for the exchange; parameters switch to the updated buffer."""
+        if not self._in_flight:
+            raise RuntimeError("end_exchange() without begin_exchange()")
+        dev = self.flat_grad.device
+        torch.cuda.current_stream(dev).wait_event(self._done)
+        self._cur ^= 1
+        self.flat_param = self._param_bufs[self._cur]
+        for p, view in zip(self.params, self._views[self._cur]):
+            p.data = view
+        self._in_flight = False
 
     def zero_grad(self):
         """Only autograd-owned gradients need clearing; sinks are overwritten by the backward."""
@@ -113,6 +196,10 @@ class FlatAdamW:
         return dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
 
     def step(self):
+        if self.overlap:
+            self.begin_exchange()
+            self.end_exchange()
+            return
         self.step_count += 1
         dev = self.flat_param.device
         if self.peer:

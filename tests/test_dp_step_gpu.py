@@ -21,7 +21,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, overlap=False):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -38,7 +38,7 @@ def _worker(rank, world, port, out):
         a = SortMLPModel(depth=4, width=96, input_dim=(3, 4, 4), num_classes=10, dropout=0.8).to(dev)
         b = copy.deepcopy(a)
         kw = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.01)
-        opt_a = FlatAdamW(a, peer_memory=True, **kw)
+        opt_a = FlatAdamW(a, peer_memory=True, overlap=overlap, **kw)
         opt_b = FlatAdamW(b, peer_memory=False, **kw)
         assert opt_a.peer and opt_a.exp_avg.numel() < opt_b.exp_avg.numel()
         gen = torch.Generator(device=dev).manual_seed(100 + rank)      # different data per rank
@@ -58,7 +58,16 @@ def _worker(rank, world, port, out):
             opt_b.flat_grad.copy_(opt_a.flat_grad)
             opt_b.all_reduce()
             opt_b.step()
-            opt_a.step()
+            if overlap:
+                before = [p.detach().clone() for p in a.parameters()]
+                opt_a.begin_exchange()
+                # work queued between begin and end still sees the old values
+                with torch.no_grad():
+                    cert = a.certified_margin(x, t, 0.03, torch.ones(1, device=dev), torch.zeros(1, device=dev))
+                ok = ok and all(torch.equal(p, q) for p, q in zip(a.parameters(), before)) and bool(cert >= 0)
+                opt_a.end_exchange()
+            else:
+                opt_a.step()
             torch.cuda.synchronize()
             for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
                 good = bool((p - q).abs().max() <= 1e-5 * max(q.abs().max().item(), 1.0))
@@ -82,4 +91,16 @@ def test_peer_memory_step_matches_all_reduce_path():
     with mp.Manager() as mgr:
         out = mgr.dict()
         mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+        assert dict(out) == {0: True, 1: True}
+
+
+def test_copy_exchange_beside_other_work_matches_all_reduce_path():
+    """overlap=True: reduce-scatter and all-gather as device-to-device copies on a side stream, the
+    parameters double-buffered; same values as the all-reduce path after every step."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(2, _free_port(), out, True), nprocs=2, join=True)
         assert dict(out) == {0: True, 1: True}
