@@ -63,3 +63,38 @@ def test_adamw_argument_checks():
     assert lib.snb_adamw_step(*args, 16, 0.1, 0.9, 0.99, 1e-8, 0.0, 0, 1.0, st) == 2     # steps count from 1
     assert lib.snb_adamw_step(None, *args[1:], 16, 0.1, 0.9, 0.99, 1e-8, 0.0, 1, 1.0, st) == 1
     assert lib.snb_adamw_step(buf.data_ptr() + 4, *args[1:], 12, 0.1, 0.9, 0.99, 1e-8, 0.0, 1, 1.0, st) == 6
+
+
+@pytest.mark.parametrize("parts", [1, 3, 8])
+def test_reduce_step_equals_plain_step_on_the_summed_gradient(parts):
+    """snb_adamw_reduce_step (partial gradient buffers, separate output buffer) against snb_adamw_step
+    on their sum."""
+    import ctypes
+    from sortnet_b200 import _lib
+    lib = _lib.load()
+    torch.manual_seed(parts)
+    n = 4 * 1000 + 4
+    w = torch.randn(n, device="cuda")
+    gs = [torch.randn(n, device="cuda") for _ in range(parts)]
+    m = torch.rand(n, device="cuda") * 0.1
+    v = torch.rand(n, device="cuda") * 0.01
+    args = (0.02, 0.9, 0.99, 1e-8, 0.01, 3, 1.0 / parts)
+    st = torch.cuda.current_stream().cuda_stream
+    w_ref, m_ref, v_ref = w.clone(), m.clone(), v.clone()
+    total = gs[0].clone()
+    for g in gs[1:]:
+        total += g
+    assert lib.snb_adamw_step(w_ref.data_ptr(), total.data_ptr(), m_ref.data_ptr(), v_ref.data_ptr(), n, *args, st) == 0
+    w_dst = torch.full_like(w, float("nan"))
+    m2, v2 = m.clone(), v.clone()
+    ptrs = (ctypes.c_void_p * parts)(*[g.data_ptr() for g in gs])
+    assert lib.snb_adamw_reduce_step(w.data_ptr(), w_dst.data_ptr(), ptrs, parts, m2.data_ptr(), v2.data_ptr(), n,
+                                     *args, st) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(w_dst, w_ref, rtol=0, atol=1e-6) and torch.allclose(m2, m_ref, atol=1e-7)
+    assert torch.allclose(v2, v_ref, atol=1e-7)
+    # argument checks
+    assert lib.snb_adamw_reduce_step(w.data_ptr(), w_dst.data_ptr(), ptrs, 17, m2.data_ptr(), v2.data_ptr(), n,
+                                     *args, st) == 3
+    assert lib.snb_adamw_reduce_step(w.data_ptr(), w_dst.data_ptr(), ptrs, parts, m2.data_ptr(), v2.data_ptr(), n + 1,
+                                     *args, st) == 2
