@@ -268,10 +268,11 @@ def run_gpu_arm(args):
             # saves (NCCL's CTAs hold SMs that the one-wave compute kernels are sized for:
             # 27.8 ms per step overlapped, 26.0 ms exposed), so the exchange is not overlapped: it
             # is part of step() (peer-memory kernel) or one flat all-reduce right before it.
-            opt.all_reduce()
-            opt.step()
+            # Same order as the overlapped path: the bound pass reads the pre-update weights.
             with torch.no_grad():
                 cert = model.certified_margin(x, t, eps_b, up, down)
+            opt.all_reduce()
+            opt.step()
         return loss, cert
 
     def barrier():
