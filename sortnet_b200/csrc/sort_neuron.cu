@@ -174,53 +174,116 @@ __global__ void __launch_bounds__(256, KMAX > 10 ? 1 : (BOUND ? 2 : 4)) sort_fwd
     }
 }
 
-// Values and positions of the K largest elements: one thread per output, the sorted list lives in
-// shared memory ([slot][thread] so that neighbouring threads hit neighbouring banks).  A value
-// enters only when it beats the smallest slot; it then moves up past every slot it is >= to, so
-// among equal values the later index takes the higher rank, as in the reference.
-constexpr int SORT_POS_THREADS = 128;
+// Values and positions of the K largest elements: one WARP per output.  The 32 lanes look at 32
+// consecutive columns of the output per step; the sorted list (ascending, K <= 25 entries of
+// (value, position word)) lives one entry per lane, and its weakest value - the entry threshold -
+// is a warp-uniform register.  A step is subtract, compare, one ballot; only when some lane holds a
+// value above the threshold does the warp insert, hit by hit in column order: broadcast the
+// candidate, count the entries it is >= to (ballot + popc), shift those down by one lane (shuffle)
+// and drop it into the freed lane.  A value enters only when it beats the weakest entry and moves
+// up past every entry it is >= to, so among equal values the later column ranks higher, exactly
+// the reference's bubble rule (sort_neuron.cu:178-187).  Insertions happen about K (1 + ln(CI / K))
+// times per output, i.e. a few dozen shuffle sequences against thousands of columns.
+//
+// CTA = 8 warps on a tile of 16 rows x 8 columns of outputs (warp w: rows 2w, 2w+1, all 8
+// columns = 16 outputs whose list entries sit in 16 register pairs per lane); the operands of 64
+// columns are staged in shared memory with cp.async, double buffered.
+constexpr int SP_ROWS = 16, SP_COLS = 8, SP_KT = 64, SP_THREADS = 256, SP_OUT = 2 * SP_COLS;
 
-__global__ void __launch_bounds__(SORT_POS_THREADS) sort_fwd_pos_kernel(const SortParams p) {
-    extern __shared__ __align__(16) float smem[];
+__global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_kernel(const SortParams p) {
+    __shared__ __align__(16) float xs[2][SP_ROWS][SP_KT];
+    __shared__ __align__(16) float ws[2][SP_COLS][SP_KT];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int m0 = blockIdx.x * SP_ROWS, n0 = blockIdx.y * SP_COLS;
     const int K = p.K;
-    float* res = smem;                                                    // [K][threads]
-    uint32_t* idx = reinterpret_cast<uint32_t*>(smem + K * SORT_POS_THREADS);  // [K][threads]
-    const int t = threadIdx.x;
-    const int n = blockIdx.x * SORT_POS_THREADS + t;
-    const int m = blockIdx.y;
-    for (int k = 0; k < K; k++) {
-        res[k * SORT_POS_THREADS + t] = 0.f;
-        idx[k * SORT_POS_THREADS + t] = 0u;
-    }
-    if (n >= p.CO) return;
-    const float* xr = p.x + (size_t)m * p.CI;
-    const float* wr = p.w + (size_t)n * p.CI;
-    float lowest = 0.f;
-    for (int c = 0; c < p.CI; c++) {
-        const float d = xr[c] - wr[c];
-        const float v = fabsf(d);
-        if (v > lowest) {
-            const uint32_t word = (uint32_t)c | (d >= 0 ? 0u : SNB_SIGN_BIT);
-            int k = 0;
-            for (; k < K - 1; k++) {
-                const float up = res[(k + 1) * SORT_POS_THREADS + t];
-                if (v < up) break;
-                res[k * SORT_POS_THREADS + t] = up;
-                idx[k * SORT_POS_THREADS + t] = idx[(k + 1) * SORT_POS_THREADS + t];
+    const int nk = (p.CI + SP_KT - 1) / SP_KT;
+
+    auto stage = [&](int kt, int st) {
+        const int k0 = kt * SP_KT;
+#pragma unroll
+        for (int r = 0; r < (SP_ROWS + SP_COLS) * SP_KT / SP_THREADS; r++) {
+            const int e = tid + r * SP_THREADS, row = e / SP_KT, k = k0 + e % SP_KT;
+            if (row < SP_ROWS) {
+                const bool ok = m0 + row < p.B && k < p.CI;
+                cp_async4(smem_u32(&xs[st][row][e % SP_KT]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 4 : 0);
+            } else {
+                const int c = row - SP_ROWS;
+                const bool ok = n0 + c < p.CO && k < p.CI;
+                cp_async4(smem_u32(&ws[st][c][e % SP_KT]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 4 : 0);
             }
-            res[k * SORT_POS_THREADS + t] = v;
-            idx[k * SORT_POS_THREADS + t] = word;
-            lowest = res[t];
+        }
+    };
+
+    float val[SP_OUT], thr[SP_OUT];
+    uint32_t word[SP_OUT];
+#pragma unroll
+    for (int o = 0; o < SP_OUT; o++) {
+        val[o] = 0.f;
+        thr[o] = 0.f;
+        word[o] = 0u;
+    }
+
+    stage(0, 0);
+    cp_async_commit();
+    for (int kt = 0; kt < nk; kt++) {
+        const int cur = kt & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (kt + 1 < nk) stage(kt + 1, cur ^ 1);
+        cp_async_commit();
+        // zero-filled padding gives |0 - 0| = 0, which never beats a threshold (>= 0)
+#pragma unroll
+        for (int h = 0; h < SP_KT / 32; h++) {
+            const int c0 = kt * SP_KT + h * 32;
+            float xv[2], wv[SP_COLS];
+#pragma unroll
+            for (int i = 0; i < 2; i++) xv[i] = xs[cur][2 * warp + i][h * 32 + lane];
+#pragma unroll
+            for (int j = 0; j < SP_COLS; j++) wv[j] = ws[cur][j][h * 32 + lane];
+#pragma unroll
+            for (int o = 0; o < SP_OUT; o++) {
+                const float d = xv[o / SP_COLS] - wv[o % SP_COLS];
+                const float v = fabsf(d);
+                uint32_t hits = __ballot_sync(0xffffffffu, v > thr[o]);
+                while (hits) {                                     // rare, warp-uniform
+                    const int src = __ffs(hits) - 1;
+                    hits &= hits - 1;
+                    const float bv = __shfl_sync(0xffffffffu, v, src);
+                    const float bd = __shfl_sync(0xffffffffu, d, src);
+                    if (bv > thr[o]) {                             // an earlier hit may have raised it
+                        const uint32_t bw = (uint32_t)(c0 + src) | (bd >= 0 ? 0u : SNB_SIGN_BIT);
+                        const int cnt = __popc(__ballot_sync(0xffffffffu, lane < K && bv >= val[o]));
+                        const float up_v = __shfl_down_sync(0xffffffffu, val[o], 1);
+                        const uint32_t up_w = __shfl_down_sync(0xffffffffu, word[o], 1);
+                        if (lane < cnt - 1) {
+                            val[o] = up_v;
+                            word[o] = up_w;
+                        } else if (lane == cnt - 1) {
+                            val[o] = bv;
+                            word[o] = bw;
+                        }
+                        thr[o] = __shfl_sync(0xffffffffu, val[o], 0);
+                    }
+                }
+            }
         }
     }
-    float ans = SNB_EPS, c = 1.0f;
-    const size_t o = (size_t)m * p.CO + n, plane = (size_t)p.B * p.CO;
-    for (int k = K - 1; k >= 0; k--) {
-        ans += res[k * SORT_POS_THREADS + t] * c * p.q;
-        c *= 1 - p.q;
-        p.pos[(size_t)(K - 1 - k) * plane + o] = (int)idx[k * SORT_POS_THREADS + t];
+    const size_t plane = (size_t)p.B * p.CO;
+#pragma unroll
+    for (int o = 0; o < SP_OUT; o++) {
+        const int m = m0 + 2 * warp + o / SP_COLS, n = n0 + o % SP_COLS;
+        // the weighted sum in rank order (rank 0 = largest = lane K-1), every lane redundantly
+        float ans = SNB_EPS, c = 1.0f;
+        for (int r = 0; r < K; r++) {
+            const float vr = __shfl_sync(0xffffffffu, val[o], K - 1 - r);
+            ans += vr * c * p.q;
+            c *= 1 - p.q;
+        }
+        if (m >= p.B || n >= p.CO) continue;
+        const size_t off = (size_t)m * p.CO + n;
+        if (lane == 0) p.y[off] = ans / (1 - c);
+        if (lane < K) p.pos[(size_t)(K - 1 - lane) * plane + off] = (int)word[o];
     }
-    p.y[o] = ans / (1 - c);
 }
 
 // Sparse backward: one CTA per batch row, grad_x of the row accumulated in shared memory.
@@ -309,8 +372,8 @@ extern "C" int snb_sort_neuron_forward(const float* x, const float* w, int B, in
     if (rc) return rc;
     if (!pos) return SNB_ERR_NULL_POINTER;
     SortParams p{x, x, w, y, nullptr, pos, B, CO, CI, K, q};
-    dim3 grid((CO + SORT_POS_THREADS - 1) / SORT_POS_THREADS, B);
-    sort_fwd_pos_kernel<<<grid, SORT_POS_THREADS, 2 * K * SORT_POS_THREADS * sizeof(float), (cudaStream_t)stream>>>(p);
+    dim3 grid((B + SP_ROWS - 1) / SP_ROWS, (CO + SP_COLS - 1) / SP_COLS);
+    sort_fwd_pos_kernel<<<grid, SP_THREADS, 0, (cudaStream_t)stream>>>(p);
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
 }
