@@ -286,6 +286,105 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_kernel(const SortP
     }
 }
 
+// The same algorithm for K <= 16 with one HALF-warp per output: lanes 0-15 work on row 2w, lanes
+// 16-31 on row 2w+1 of the same output column, 16 columns per step each, all shuffles 16 wide.  The
+// two outputs of a warp insert side by side (a round of the insertion loop serves one candidate of
+// each half), which halves the serial insertion rounds that dominate the full-warp kernel.
+__global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_half_kernel(const SortParams p) {
+    __shared__ __align__(16) float xs[2][SP_ROWS][SP_KT];
+    __shared__ __align__(16) float ws[2][SP_COLS][SP_KT];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = lane >> 4, hl = lane & 15;
+    const int m0 = blockIdx.x * SP_ROWS, n0 = blockIdx.y * SP_COLS;
+    const int K = p.K;
+    const int nk = (p.CI + SP_KT - 1) / SP_KT;
+
+    auto stage = [&](int kt, int st) {
+        const int k0 = kt * SP_KT;
+#pragma unroll
+        for (int r = 0; r < (SP_ROWS + SP_COLS) * SP_KT / SP_THREADS; r++) {
+            const int e = tid + r * SP_THREADS, row = e / SP_KT, k = k0 + e % SP_KT;
+            if (row < SP_ROWS) {
+                const bool ok = m0 + row < p.B && k < p.CI;
+                cp_async4(smem_u32(&xs[st][row][e % SP_KT]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 4 : 0);
+            } else {
+                const int c = row - SP_ROWS;
+                const bool ok = n0 + c < p.CO && k < p.CI;
+                cp_async4(smem_u32(&ws[st][c][e % SP_KT]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 4 : 0);
+            }
+        }
+    };
+
+    float val[SP_COLS], thr[SP_COLS];   // entry hl of the list of output (row 2w + half, column j)
+    uint32_t word[SP_COLS];
+#pragma unroll
+    for (int j = 0; j < SP_COLS; j++) {
+        val[j] = 0.f;
+        thr[j] = 0.f;
+        word[j] = 0u;
+    }
+    const uint32_t my_half = 0xffffu << (16 * half);
+
+    stage(0, 0);
+    cp_async_commit();
+    for (int kt = 0; kt < nk; kt++) {
+        const int cur = kt & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (kt + 1 < nk) stage(kt + 1, cur ^ 1);
+        cp_async_commit();
+#pragma unroll
+        for (int t = 0; t < SP_KT / 16; t++) {
+            const int c0 = kt * SP_KT + t * 16;
+            const float xv = xs[cur][2 * warp + half][t * 16 + hl];
+#pragma unroll
+            for (int j = 0; j < SP_COLS; j++) {
+                const float d = xv - ws[cur][j][t * 16 + hl];
+                const float v = fabsf(d);
+                uint32_t hits = __ballot_sync(0xffffffffu, v > thr[j]);
+                while (hits) {                                      // rare, warp-uniform
+                    const uint32_t mine = hits & my_half;
+                    const int src = mine ? __ffs(mine) - 1 : lane;  // absolute lane of this half's next candidate
+                    // drop the lowest candidate of each half
+                    const uint32_t lo = hits & 0xffffu, hi = hits & 0xffff0000u;
+                    hits = (lo & (lo - 1)) | (hi & (hi - 1));
+                    const float bv = __shfl_sync(0xffffffffu, v, src);
+                    const float bd = __shfl_sync(0xffffffffu, d, src);
+                    const bool enter = mine != 0u && bv > thr[j];   // uniform within the half
+                    const uint32_t bal = __ballot_sync(0xffffffffu, enter && hl < K && bv >= val[j]);
+                    const int cnt = __popc(bal & my_half);
+                    const float up_v = __shfl_down_sync(0xffffffffu, val[j], 1, 16);
+                    const uint32_t up_w = __shfl_down_sync(0xffffffffu, word[j], 1, 16);
+                    if (enter) {
+                        if (hl < cnt - 1) {
+                            val[j] = up_v;
+                            word[j] = up_w;
+                        } else if (hl == cnt - 1) {
+                            val[j] = bv;
+                            word[j] = (uint32_t)(c0 + (src & 15)) | (bd >= 0 ? 0u : SNB_SIGN_BIT);
+                        }
+                    }
+                    thr[j] = __shfl_sync(0xffffffffu, val[j], 0, 16);
+                }
+            }
+        }
+    }
+    const size_t plane = (size_t)p.B * p.CO;
+#pragma unroll
+    for (int j = 0; j < SP_COLS; j++) {
+        const int m = m0 + 2 * warp + half, n = n0 + j;
+        float ans = SNB_EPS, c = 1.0f;
+        for (int r = 0; r < K; r++) {
+            const float vr = __shfl_sync(0xffffffffu, val[j], K - 1 - r, 16);
+            ans += vr * c * p.q;
+            c *= 1 - p.q;
+        }
+        if (m >= p.B || n >= p.CO) continue;
+        const size_t off = (size_t)m * p.CO + n;
+        if (hl == 0) p.y[off] = ans / (1 - c);
+        if (hl < K) p.pos[(size_t)(K - 1 - hl) * plane + off] = (int)word[j];
+    }
+}
+
 // Sparse backward: one CTA per batch row, grad_x of the row accumulated in shared memory.
 __global__ void __launch_bounds__(256) sort_bwd_kernel(const float* __restrict__ g, const int* __restrict__ pos,
                                                        int B, int CO, int CI, int K, float q, float c0,
@@ -373,7 +472,8 @@ extern "C" int snb_sort_neuron_forward(const float* x, const float* w, int B, in
     if (!pos) return SNB_ERR_NULL_POINTER;
     SortParams p{x, x, w, y, nullptr, pos, B, CO, CI, K, q};
     dim3 grid((B + SP_ROWS - 1) / SP_ROWS, (CO + SP_COLS - 1) / SP_COLS);
-    sort_fwd_pos_kernel<<<grid, SP_THREADS, 0, (cudaStream_t)stream>>>(p);
+    if (K <= 16) sort_fwd_pos_half_kernel<<<grid, SP_THREADS, 0, (cudaStream_t)stream>>>(p);
+    else sort_fwd_pos_kernel<<<grid, SP_THREADS, 0, (cudaStream_t)stream>>>(p);
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
 }

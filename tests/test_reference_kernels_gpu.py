@@ -230,7 +230,7 @@ def test_timings_against_the_reference_kernels(ref, capsys):
         for name, t_ref, t_mine in rows:
             print("%-48s reference %8.3f ms   this library %8.3f ms   x%.2f" % (name, t_ref, t_mine, t_ref / t_mine))
     for name, t_ref, t_mine in rows:
-        # the position-recording sort forward (one warp per output, lists spread over the lanes) is
+        # the position-recording sort forward (one half-warp per output, lists spread over the lanes) is
         # the one entry point that does not beat the reference's kernel yet (about 1.2x its time)
         limit = 1.5 if "with positions" in name else 1.25
         assert t_mine <= limit * t_ref, name
