@@ -13,7 +13,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REF = os.environ.get("SORTNET_REFERENCE", "/root/reference")
+# checkout of zbh2047/SortNet: $SORTNET_REFERENCE, else a directory "reference" beside this repository
+REF = os.environ.get("SORTNET_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 SOURCES = ["norm_dist.cpp", "inf_dist_cuda.cu", "norm_dist_cuda.cu", "bound_inf_dist_cuda.cu", "sort_neuron.cu"]
 
 

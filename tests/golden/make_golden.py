@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the reference's own Python code.
 
 Run once, in a container that has the reference checkout (path in $SORTNET_REFERENCE, default
-the REF constant below):   python tests/golden/make_golden.py
+a directory `reference` beside this repository):   python tests/golden/make_golden.py
 
 The reference's pure-PyTorch branches are imported unmodified with a CPU stand-in for
 its CUDA extension module, evaluated on CPU on small seeded inputs, and their outputs and
@@ -22,10 +22,11 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("SORTNET_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 ROOT = os.path.dirname(os.path.dirname(HERE))
+# checkout of zbh2047/SortNet: $SORTNET_REFERENCE, else a directory "reference" beside this repository
+REF = os.environ.get("SORTNET_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 sys.path.insert(0, ROOT)
 from oracle import ref_module  # noqa: E402
 
