@@ -212,7 +212,10 @@ def run_gpu_arm(args):
     exchange = "none (single GPU)"
     if peer_step:
         try:
-            copy_exchange = os.environ.get("SNB_COPY_EXCHANGE", "1") != "0"
+            # the copy-based exchange has been run and checked on 2 GPUs only (no larger box was
+            # free when it was written), so it is the default there; larger worlds keep the fused
+            # kernel, which has been measured at N = 4 and 8, unless SNB_COPY_EXCHANGE=1 asks for it
+            copy_exchange = os.environ.get("SNB_COPY_EXCHANGE", "1" if world == 2 else "0") != "0"
             opt = FlatAdamW(model, peer_memory=True, overlap=copy_exchange, **adam)
             exchange = ("device-to-device copies over NVLink (reduce-scatter, all-gather) + local sum/AdamW kernel, "
                         "all beside the bound pass" if copy_exchange else
