@@ -289,7 +289,17 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_kernel(const SortP
 // The same algorithm for K <= 16 with one HALF-warp per output: lanes 0-15 work on row 2w, lanes
 // 16-31 on row 2w+1 of the same output column, 16 columns per step each, all shuffles 16 wide.  The
 // two outputs of a warp insert side by side (a round of the insertion loop serves one candidate of
-// each half), which halves the serial insertion rounds that dominate the full-warp kernel.
+// each half).
+//
+// Insertions are what this kernel pays for, and an online top-K makes about K (1 + ln(CI / K)) of
+// them per output because its threshold starts at zero.  So the columns are swept twice.  Sweep 1
+// only takes, per lane, the maximum over the lane's columns (c = hl mod 16): 16 maxima of disjoint
+// column sets, i.e. 16 distinct elements, of which the K-th largest (K <= 16) is a value T0 that at
+// least K elements reach - a lower bound of the final threshold.  Sweep 2 is the algorithm above
+// with the entry threshold floored just below T0, so the elements that would have entered the
+// list only to be pushed out again are never inserted.  Elements >= T0 meet exactly the
+// comparisons they meet in the unseeded scan (anything below T0 in the list loses to them either
+// way), so values, positions and the tie rules are unchanged.
 __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_half_kernel(const SortParams p) {
     __shared__ __align__(16) float xs[2][SP_ROWS][SP_KT];
     __shared__ __align__(16) float ws[2][SP_COLS][SP_KT];
@@ -324,6 +334,10 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_half_kernel(const 
     }
     const uint32_t my_half = 0xffffu << (16 * half);
 
+    // ---- sweep 1: lane maxima -> T0 -> threshold floor ---------------------------------------
+    float seed[SP_COLS];
+#pragma unroll
+    for (int j = 0; j < SP_COLS; j++) seed[j] = 0.f;
     stage(0, 0);
     cp_async_commit();
     for (int kt = 0; kt < nk; kt++) {
@@ -334,36 +348,77 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_half_kernel(const 
         cp_async_commit();
 #pragma unroll
         for (int t = 0; t < SP_KT / 16; t++) {
-            const int c0 = kt * SP_KT + t * 16;
             const float xv = xs[cur][2 * warp + half][t * 16 + hl];
 #pragma unroll
+            for (int j = 0; j < SP_COLS; j++) seed[j] = fmaxf(seed[j], fabsf(xv - ws[cur][j][t * 16 + hl]));
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < SP_COLS; j++) {
+        // rank of this lane's maximum among the 16 of its half (ties: lower lane first)
+        int rank = 0;
+#pragma unroll
+        for (int t = 0; t < 16; t++) {
+            const float other = __shfl_sync(0xffffffffu, seed[j], t, 16);
+            rank += (other > seed[j]) || (other == seed[j] && t < hl);
+        }
+        const uint32_t pick = __ballot_sync(0xffffffffu, rank == K - 1) & my_half;
+        const float t0 = __shfl_sync(0xffffffffu, seed[j], __ffs(pick) - 1);
+        // largest float below T0 (0 stays 0: nothing enters on a zero difference anyway)
+        seed[j] = t0 > 0.f ? __int_as_float(__float_as_int(t0) - 1) : 0.f;
+        thr[j] = seed[j];
+    }
+    __syncthreads();                           // everyone is done with the last tile of sweep 1
+
+    // ---- sweep 2: the insertion scan ----------------------------------------------------------
+    stage(0, 0);
+    cp_async_commit();
+    for (int kt = 0; kt < nk; kt++) {
+        const int cur = kt & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (kt + 1 < nk) stage(kt + 1, cur ^ 1);
+        cp_async_commit();
+#pragma unroll 1                               // one copy of the insertion loops (instruction cache)
+        for (int t = 0; t < SP_KT / 32; t++) {
+            // a lane looks at two columns per step (c and c + 16); one vote on the larger magnitude
+            // tells whether this output has a candidate at all
+            const int c0 = kt * SP_KT + t * 32;
+            const float xa = xs[cur][2 * warp + half][t * 32 + hl], xb = xs[cur][2 * warp + half][t * 32 + 16 + hl];
+#pragma unroll
             for (int j = 0; j < SP_COLS; j++) {
-                const float d = xv - ws[cur][j][t * 16 + hl];
-                const float v = fabsf(d);
-                uint32_t hits = __ballot_sync(0xffffffffu, v > thr[j]);
-                while (hits) {                                      // rare, warp-uniform
-                    const uint32_t mine = hits & my_half;
-                    const int src = mine ? __ffs(mine) - 1 : lane;  // absolute lane of this half's next candidate
-                    // drop the lowest candidate of each half
-                    const uint32_t lo = hits & 0xffffu, hi = hits & 0xffff0000u;
-                    hits = (lo & (lo - 1)) | (hi & (hi - 1));
-                    const float bv = __shfl_sync(0xffffffffu, v, src);
-                    const float bd = __shfl_sync(0xffffffffu, d, src);
-                    const bool enter = mine != 0u && bv > thr[j];   // uniform within the half
-                    const uint32_t bal = __ballot_sync(0xffffffffu, enter && hl < K && bv >= val[j]);
-                    const int cnt = __popc(bal & my_half);
-                    const float up_v = __shfl_down_sync(0xffffffffu, val[j], 1, 16);
-                    const uint32_t up_w = __shfl_down_sync(0xffffffffu, word[j], 1, 16);
-                    if (enter) {
-                        if (hl < cnt - 1) {
-                            val[j] = up_v;
-                            word[j] = up_w;
-                        } else if (hl == cnt - 1) {
-                            val[j] = bv;
-                            word[j] = (uint32_t)(c0 + (src & 15)) | (bd >= 0 ? 0u : SNB_SIGN_BIT);
+                const float da = xa - ws[cur][j][t * 32 + hl], db = xb - ws[cur][j][t * 32 + 16 + hl];
+                if (!__any_sync(0xffffffffu, fmaxf(fabsf(da), fabsf(db)) > thr[j])) continue;
+                // rare, warp-uniform: the candidates of the first 16 columns in order, then the next 16
+#pragma unroll 1
+                for (int sub = 0; sub < 2; sub++) {
+                    const float d = sub ? db : da;
+                    const float v = fabsf(d);
+                    uint32_t hits = __ballot_sync(0xffffffffu, v > thr[j]);
+                    while (hits) {
+                        const uint32_t mine = hits & my_half;
+                        const int src = mine ? __ffs(mine) - 1 : lane;  // absolute lane of this half's next candidate
+                        // drop the lowest candidate of each half
+                        const uint32_t lo = hits & 0xffffu, hi = hits & 0xffff0000u;
+                        hits = (lo & (lo - 1)) | (hi & (hi - 1));
+                        const float bv = __shfl_sync(0xffffffffu, v, src);
+                        const float bd = __shfl_sync(0xffffffffu, d, src);
+                        const bool enter = mine != 0u && bv > thr[j];   // uniform within the half
+                        const uint32_t bal = __ballot_sync(0xffffffffu, enter && hl < K && bv >= val[j]);
+                        const int cnt = __popc(bal & my_half);
+                        const float up_v = __shfl_down_sync(0xffffffffu, val[j], 1, 16);
+                        const uint32_t up_w = __shfl_down_sync(0xffffffffu, word[j], 1, 16);
+                        if (enter) {
+                            if (hl < cnt - 1) {
+                                val[j] = up_v;
+                                word[j] = up_w;
+                            } else if (hl == cnt - 1) {
+                                val[j] = bv;
+                                word[j] = (uint32_t)(c0 + sub * 16 + (src & 15)) | (bd >= 0 ? 0u : SNB_SIGN_BIT);
+                            }
                         }
+                        thr[j] = fmaxf(seed[j], __shfl_sync(0xffffffffu, val[j], 0, 16));
                     }
-                    thr[j] = __shfl_sync(0xffffffffu, val[j], 0, 16);
                 }
             }
         }

@@ -173,8 +173,7 @@ def _time(fn, n=3, warm=1):
 def test_timings_against_the_reference_kernels(ref, capsys):
     """GPU comparator: the reference's kernels and these on the widest layer of the benchmark
     workload (B = 512, 5120 x 5120 weights, keep 0.9).  Prints a table (run with -s) and only
-    gates that nothing here is slower than the reference's kernel by more than measurement noise
-    (one exception, stated at the assertion)."""
+    gates that nothing here is slower than the reference's kernel by more than measurement noise."""
     from sortnet_b200 import norm_dist_cuda as C
     from sortnet_b200.layers import sample_mask
     dev = "cuda"
@@ -230,10 +229,7 @@ def test_timings_against_the_reference_kernels(ref, capsys):
         for name, t_ref, t_mine in rows:
             print("%-48s reference %8.3f ms   this library %8.3f ms   x%.2f" % (name, t_ref, t_mine, t_ref / t_mine))
     for name, t_ref, t_mine in rows:
-        # the position-recording sort forward (one half-warp per output, lists spread over the lanes) is
-        # the one entry point that does not beat the reference's kernel yet (about 1.2x its time)
-        limit = 1.5 if "with positions" in name else 1.25
-        assert t_mine <= limit * t_ref, name
+        assert t_mine <= 1.25 * t_ref, name
 
 
 @pytest.mark.parametrize("B,G,CIg,COg,HW,keep", [(37, 2, 24, 20, 3, None), (64, 3, 32, 48, 4, None),
