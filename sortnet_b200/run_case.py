@@ -4,7 +4,8 @@
 
 Used for quick timing of a single kernel and as the small, self-terminating command that
 profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_nograd,
-inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_shift, probe (hardware probes).
+inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_shift, sort_nograd,
+sort_bound, sort_fwd (values + positions), sort_bwd (K = 10, q = 0.9), probe (hardware probes).
 """
 import argparse
 
@@ -102,6 +103,11 @@ def main():
         C.inf_dist_forward(x, w, y, pos, 1, ci, co)
     if a.op in ("lp_bwd", "lp_bwd_x"):
         C.norm_dist_forward(x, w, y, 1, a.p, ci, co)
+    SORT_K, SORT_Q = 10, 0.9
+    posk = None
+    if a.op in ("sort_fwd", "sort_bwd"):
+        posk = torch.zeros(SORT_K, a.B, co_n, 1, device=dev, dtype=torch.int32)
+        C.sort_neuron_forward(x, w, y, posk, 1, SORT_Q, SORT_K)
 
     def run():
         if a.op == "inf_fwd":
@@ -120,6 +126,14 @@ def main():
             C.norm_dist_backward_input_weight(g, x, w, y, gx, gw, 1, a.p, ci, co)
         elif a.op == "lp_bwd_x":
             C.norm_dist_backward_input(g, x, w, y, gx, 1, a.p, ci, co)
+        elif a.op == "sort_nograd":
+            C.sort_neuron_forward_nograd(x, w, y, 1, SORT_Q, SORT_K)
+        elif a.op == "sort_bound":
+            C.bound_sort_neuron_forward(xl, xu, w, y, y2, 1, SORT_Q, SORT_K)
+        elif a.op == "sort_fwd":
+            C.sort_neuron_forward(x, w, y, posk, 1, SORT_Q, SORT_K)
+        elif a.op == "sort_bwd":
+            C.sort_neuron_backward_input_weight(g, posk, gx, gw, 1, SORT_Q, SORT_K)
         elif a.op == "mean_shift":
             C.mean_shift_stats(y.copy_(g), co, mean, None, 0.1)
             C.mean_shift_apply(y, mean, co, y)
