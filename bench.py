@@ -457,6 +457,30 @@ def run_gpu_arm(args):
                 lp["p=%g" % p_val] = {"ms_per_step": round(t_ms, 3), "samples_per_s": round(B / (t_ms * 1e-3), 1)}
             model.set_p(WORKLOAD["p"])
             line["lp_training_step"] = lp
+        if world == 1:
+            # the HBM-bound kernel of the step (fused AdamW: 4 reads + 3 writes of 4 bytes per parameter)
+            # against the measured copy bandwidth of this pool's B200s
+            hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+            try:
+                with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+                    hbm_peak = float(json.load(f)["hbm_gbs"])
+                    hbm_src = "MEASURED_PEAKS.json hbm_gbs (STREAM-style copy)"
+            except Exception:
+                pass
+            a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            opt.step()
+            torch.cuda.synchronize()
+            a_ev.record()
+            for _ in range(5):
+                opt.step()
+            b_ev.record()
+            torch.cuda.synchronize()
+            adam_ms = a_ev.elapsed_time(b_ev) / 5
+            adam_gbs = 28.0 * opt.numel / (adam_ms * 1e-3) * 1e-9
+            line["roofline_hbm"] = {"bound": "hbm", "kernel": "adamw_kernel", "ms_per_launch": round(adam_ms, 4),
+                                    "achieved": round(adam_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
+                                    "frac": round(adam_gbs / hbm_peak, 4), "traffic": None,
+                                    "algorithmic_bytes": 28 * opt.numel, "peak_source": hbm_src}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cpu_step_seconds(64, threads)                      # warm-up
