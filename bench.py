@@ -178,6 +178,12 @@ def run_gpu_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries exactly one JSON line.  Libraries write there too (NCCL prints its version
+    # banner with printf when NCCL_DEBUG asks for it), so file descriptor 1 points at stderr for the
+    # duration of the run and the result goes to the saved descriptor.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -491,7 +497,8 @@ def run_gpu_arm(args):
                           "fwd + autograd bwd + dense interval-bound fwd in PyTorch on the host (%.1f s), each "
                           "part scaled by outputs_full / outputs_timed" % info["raw_seconds"],
             }
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(result_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 
