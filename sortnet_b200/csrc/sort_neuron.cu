@@ -308,8 +308,24 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_half_kernel(const 
     const int K = p.K;
     const int nk = (p.CI + SP_KT - 1) / SP_KT;
 
+    const bool vec = (p.CI % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.w)) & 15u) == 0;
     auto stage = [&](int kt, int st) {
         const int k0 = kt * SP_KT;
+        if (vec) {   // 16-byte copies: (16 + 8) rows x 16 quads
+#pragma unroll
+            for (int r = 0; r < ((SP_ROWS + SP_COLS) * SP_KT / 4 + SP_THREADS - 1) / SP_THREADS; r++) {
+                const int e = tid + r * SP_THREADS, row = e / (SP_KT / 4), kq = (e % (SP_KT / 4)) * 4, k = k0 + kq;
+                if (row < SP_ROWS) {
+                    const bool ok = m0 + row < p.B && k < p.CI;
+                    cp_async16(smem_u32(&xs[st][row][kq]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 16 : 0);
+                } else if (row < SP_ROWS + SP_COLS) {
+                    const int c = row - SP_ROWS;
+                    const bool ok = n0 + c < p.CO && k < p.CI;
+                    cp_async16(smem_u32(&ws[st][c][kq]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 16 : 0);
+                }
+            }
+            return;
+        }
 #pragma unroll
         for (int r = 0; r < (SP_ROWS + SP_COLS) * SP_KT / SP_THREADS; r++) {
             const int e = tid + r * SP_THREADS, row = e / SP_KT, k = k0 + e % SP_KT;
