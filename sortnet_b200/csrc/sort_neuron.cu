@@ -190,6 +190,40 @@ __global__ void __launch_bounds__(256, KMAX > 10 ? 1 : (BOUND ? 2 : 4)) sort_fwd
 // columns are staged in shared memory with cp.async, double buffered.
 constexpr int SP_ROWS = 16, SP_COLS = 8, SP_KT = 64, SP_THREADS = 256, SP_OUT = 2 * SP_COLS;
 
+// Operands of one k-tile -> shared memory: 16 rows of x and 8 rows of w, 64 columns each, zero-filled
+// past the edges; 16-byte copies when the rows are 16-byte aligned, else 4-byte copies.
+__device__ __forceinline__ void sp_stage(const SortParams& p, float (*xs)[SP_KT], float (*ws)[SP_KT], int kt,
+                                         int m0, int n0, int tid, bool vec) {
+    const int k0 = kt * SP_KT;
+    if (vec) {
+#pragma unroll
+        for (int r = 0; r < ((SP_ROWS + SP_COLS) * SP_KT / 4 + SP_THREADS - 1) / SP_THREADS; r++) {
+            const int e = tid + r * SP_THREADS, row = e / (SP_KT / 4), kq = (e % (SP_KT / 4)) * 4, k = k0 + kq;
+            if (row < SP_ROWS) {
+                const bool ok = m0 + row < p.B && k < p.CI;
+                cp_async16(smem_u32(&xs[row][kq]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 16 : 0);
+            } else if (row < SP_ROWS + SP_COLS) {
+                const int c = row - SP_ROWS;
+                const bool ok = n0 + c < p.CO && k < p.CI;
+                cp_async16(smem_u32(&ws[c][kq]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 16 : 0);
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int r = 0; r < (SP_ROWS + SP_COLS) * SP_KT / SP_THREADS; r++) {
+        const int e = tid + r * SP_THREADS, row = e / SP_KT, k = k0 + e % SP_KT;
+        if (row < SP_ROWS) {
+            const bool ok = m0 + row < p.B && k < p.CI;
+            cp_async4(smem_u32(&xs[row][e % SP_KT]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 4 : 0);
+        } else {
+            const int c = row - SP_ROWS;
+            const bool ok = n0 + c < p.CO && k < p.CI;
+            cp_async4(smem_u32(&ws[c][e % SP_KT]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 4 : 0);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_kernel(const SortParams p) {
     __shared__ __align__(16) float xs[2][SP_ROWS][SP_KT];
     __shared__ __align__(16) float ws[2][SP_COLS][SP_KT];
@@ -198,21 +232,8 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_kernel(const SortP
     const int K = p.K;
     const int nk = (p.CI + SP_KT - 1) / SP_KT;
 
-    auto stage = [&](int kt, int st) {
-        const int k0 = kt * SP_KT;
-#pragma unroll
-        for (int r = 0; r < (SP_ROWS + SP_COLS) * SP_KT / SP_THREADS; r++) {
-            const int e = tid + r * SP_THREADS, row = e / SP_KT, k = k0 + e % SP_KT;
-            if (row < SP_ROWS) {
-                const bool ok = m0 + row < p.B && k < p.CI;
-                cp_async4(smem_u32(&xs[st][row][e % SP_KT]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 4 : 0);
-            } else {
-                const int c = row - SP_ROWS;
-                const bool ok = n0 + c < p.CO && k < p.CI;
-                cp_async4(smem_u32(&ws[st][c][e % SP_KT]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 4 : 0);
-            }
-        }
-    };
+    const bool vec = (p.CI % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.w)) & 15u) == 0;
+    auto stage = [&](int kt, int st) { sp_stage(p, xs[st], ws[st], kt, m0, n0, tid, vec); };
 
     float val[SP_OUT], thr[SP_OUT];
     uint32_t word[SP_OUT];
@@ -309,36 +330,7 @@ __global__ void __launch_bounds__(SP_THREADS, 4) sort_fwd_pos_half_kernel(const 
     const int nk = (p.CI + SP_KT - 1) / SP_KT;
 
     const bool vec = (p.CI % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.w)) & 15u) == 0;
-    auto stage = [&](int kt, int st) {
-        const int k0 = kt * SP_KT;
-        if (vec) {   // 16-byte copies: (16 + 8) rows x 16 quads
-#pragma unroll
-            for (int r = 0; r < ((SP_ROWS + SP_COLS) * SP_KT / 4 + SP_THREADS - 1) / SP_THREADS; r++) {
-                const int e = tid + r * SP_THREADS, row = e / (SP_KT / 4), kq = (e % (SP_KT / 4)) * 4, k = k0 + kq;
-                if (row < SP_ROWS) {
-                    const bool ok = m0 + row < p.B && k < p.CI;
-                    cp_async16(smem_u32(&xs[st][row][kq]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 16 : 0);
-                } else if (row < SP_ROWS + SP_COLS) {
-                    const int c = row - SP_ROWS;
-                    const bool ok = n0 + c < p.CO && k < p.CI;
-                    cp_async16(smem_u32(&ws[st][c][kq]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 16 : 0);
-                }
-            }
-            return;
-        }
-#pragma unroll
-        for (int r = 0; r < (SP_ROWS + SP_COLS) * SP_KT / SP_THREADS; r++) {
-            const int e = tid + r * SP_THREADS, row = e / SP_KT, k = k0 + e % SP_KT;
-            if (row < SP_ROWS) {
-                const bool ok = m0 + row < p.B && k < p.CI;
-                cp_async4(smem_u32(&xs[st][row][e % SP_KT]), ok ? p.x + (size_t)(m0 + row) * p.CI + k : p.x, ok ? 4 : 0);
-            } else {
-                const int c = row - SP_ROWS;
-                const bool ok = n0 + c < p.CO && k < p.CI;
-                cp_async4(smem_u32(&ws[st][c][e % SP_KT]), ok ? p.w + (size_t)(n0 + c) * p.CI + k : p.w, ok ? 4 : 0);
-            }
-        }
-    };
+    auto stage = [&](int kt, int st) { sp_stage(p, xs[st], ws[st], kt, m0, n0, tid, vec); };
 
     float val[SP_COLS], thr[SP_COLS];   // entry hl of the list of output (row 2w + half, column j)
     uint32_t word[SP_COLS];
