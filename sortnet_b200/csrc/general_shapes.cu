@@ -83,7 +83,24 @@ class Arena {
         total_ += (bytes + 255) & ~(size_t)255;
         return o;
     }
-    cudaError_t commit() { return cudaMallocAsync((void**)&base_, total_ ? total_ : 256, st_); }
+    cudaError_t commit() {
+        // keep freed scratch in the device's default pool instead of handing it back to the driver at
+        // the next synchronisation (the default release threshold is 0): the next call reuses it
+        static bool kept[64] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (!kept[dev & 63]) {
+            cudaMemPool_t pool;
+            e = cudaDeviceGetDefaultMemPool(&pool, dev);
+            if (e != cudaSuccess) return e;
+            unsigned long long keep = ~0ull;
+            e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+            if (e != cudaSuccess) return e;
+            kept[dev & 63] = true;
+        }
+        return cudaMallocAsync((void**)&base_, total_ ? total_ : 256, st_);
+    }
     template <class T>
     T* at(size_t off) const { return reinterpret_cast<T*>(base_ + off); }
 
