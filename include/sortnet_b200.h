@@ -20,7 +20,8 @@
  *     SortNet layer) run the tiled kernels directly.  Any other G >= 1, HW >= 1 is served by
  *     repacking the operands into G row-major 2-D problems, running the same kernels on each and
  *     scattering the results back; that path takes its scratch from the stream-ordered allocator
- *     (cudaMallocAsync / cudaFreeAsync on `stream`), about two copies of the operands.
+ *     (a memory pool of the library's own, cudaMallocFromPoolAsync / cudaFreeAsync on `stream`), about
+ *     two copies of the operands.
  *   - Index lists (`w_index_ci` [S, G, CI / G], `w_index_co` [S, G, CO / G], S = ceil(B / 32),
  *     int32, may be NULL) select, for each 32-row sub-batch, the columns / rows of w that the
  *     compact x / y correspond to (core/models/norm_dist.py:14-17; inf_dist_cuda.cu:123,166-169).

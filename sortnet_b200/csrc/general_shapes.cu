@@ -12,7 +12,8 @@
 //
 // The repacking moves O(B * HW * (CI + CO)) words next to O(B * HW * CI * CO / G) arithmetic, so
 // plain one-word-per-thread kernels are enough.  Scratch comes from the stream-ordered allocator
-// (cudaMallocAsync / cudaFreeAsync on the caller's stream); the 2-D fast path never gets here.
+// (a pool of this library's own, cudaMallocFromPoolAsync / cudaFreeAsync on the caller's stream);
+// the 2-D fast path never gets here.
 #include "general_shapes.h"
 
 #include "../../include/sortnet_b200.h"
@@ -84,22 +85,30 @@ class Arena {
         return o;
     }
     cudaError_t commit() {
-        // keep freed scratch in the device's default pool instead of handing it back to the driver at
-        // the next synchronisation (the default release threshold is 0): the next call reuses it
-        static bool kept[64] = {};
+        // A memory pool of this library's own per device, with the release threshold raised so that
+        // freed scratch stays in the pool and the next call reuses it (a pool with the default
+        // threshold of 0 hands its memory back to the driver at the next synchronisation, which made
+        // every call pay for fresh physical memory).  The device's default pool is left alone.
+        static cudaMemPool_t pools[64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
-        if (!kept[dev & 63]) {
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (!pools[dev]) {
+            cudaMemPoolProps props = {};
+            props.allocType = cudaMemAllocationTypePinned;
+            props.handleTypes = cudaMemHandleTypeNone;
+            props.location.type = cudaMemLocationTypeDevice;
+            props.location.id = dev;
             cudaMemPool_t pool;
-            e = cudaDeviceGetDefaultMemPool(&pool, dev);
+            e = cudaMemPoolCreate(&pool, &props);
             if (e != cudaSuccess) return e;
             unsigned long long keep = ~0ull;
             e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
             if (e != cudaSuccess) return e;
-            kept[dev & 63] = true;
+            pools[dev] = pool;
         }
-        return cudaMallocAsync((void**)&base_, total_ ? total_ : 256, st_);
+        return cudaMallocFromPoolAsync((void**)&base_, total_ ? total_ : 256, pools[dev], st_);
     }
     template <class T>
     T* at(size_t off) const { return reinterpret_cast<T*>(base_ + off); }
