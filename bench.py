@@ -6,101 +6,131 @@ interval-bound (certification) forward, batch 512 per GPU.
     python bench.py --impl reference ...                      (the CPU arm, see below)
 
 A step = masked l-inf forward of the 6-layer SortNet-MLP (fresh sub-batch masks), mixture
-loss, sparse backward, one flat gradient all-reduce over NCCL (N > 1), fused AdamW, then the l-inf interval
-bound forward through all layers under no_grad.  Inputs are seeded synthetic tensors with the
-CIFAR-10 shapes ([512, 3, 32, 32] uniform in [0, 1), labels uniform in [0, 10)), weights
-N(0, 1); the per-GPU batch is fixed as N grows (weak scaling).
+loss, sparse backward, the gradient exchange between ranks (N > 1), fused AdamW, and the l-inf
+interval-bound forward through all layers under no_grad.  Inputs are seeded synthetic tensors
+with the CIFAR-10 shapes ([512, 3, 32, 32] uniform in [0, 1), labels uniform in [0, 10)),
+weights N(0, 1); the per-GPU batch is fixed as N grows (weak scaling).
 
 Prints one JSON line (rank 0).  `value` is samples/s with inputs resident in HBM; `e2e` is the
 same step fed from pinned host memory with the loss read back every step; `roofline` is the
-dominant kernel's FP32 fraction with the kernel time taken live from CUDA events around its
-launches in the timed region; `cpu_baseline` is the reference's PyTorch way of computing the
-same step, restated in oracle/torch_fallback.py, timed on this host's cores.
+dominant kernel's FP32 fraction, its time taken from CUDA events around its launches in a short
+separate pass (the headline regions run without those events); `cpu_baseline` is the
+reference's PyTorch way of computing the same step timed on this host's cores.  Secondary
+blocks (never the headline): `gpu_comparator` (the same step through the reference's own model
+code and CUDA kernels compiled for sm_100a, when oracle/_ref holds them), `configs[0]`,
+`configs[2]`, `configs[3]` (the other single-GPU configurations), `lp_training_step` (finite p),
+and at N > 1 `dp_check` (replica identity + one step against all-reduce + AdamW),
+`strong_scaling` (global batch 512 split over the ranks) and at N = 8 `configs[4]`.
 """
 import argparse
+import copy
+import ctypes
+import gc
 import json
 import math
 import os
 import statistics
 import sys
 import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOAD = {
-    "name": "SortNet-MLP CIFAR-shaped fwd+bwd+IBP",
-    "input_dim": (3, 32, 32), "depth": 6, "width": 5120, "classes": 10, "keep": 0.9,
-    "batch_per_gpu": 512, "p": float("inf"), "eps_train": 8 / 255, "eps_bound": 8 / 255,
-}
+INF = float("inf")
 
+# The configurations of this project, numbered as in its configuration list (0 = single layer).
+CONFIGS = {
+    1: dict(label="configs[1]: SortNet-MLP (5 x 5120 + head 10), CIFAR-shaped input [512, 3072] per GPU, "
+                  "keep 0.9 sub-batch masks, p = inf, train eps 8/255, IBP eps 8/255",
+            input_dim=(3, 32, 32), depth=6, width=5120, classes=10, keep=0.9, batch=512, eps=8 / 255),
+    2: dict(label="configs[2]: pure l-inf net, 6 x 5120 with mean shift + head 10, no masks, input [512, 3072], eps 2/255",
+            input_dim=(3, 32, 32), depth=7, width=5120, classes=10, keep=1.0, batch=512, eps=2 / 255),
+    3: dict(label="configs[3]: SortNet-MLP (5 x 5120 + head 200), input [512, 12288], keep 0.9, eps 1/255",
+            input_dim=(3, 64, 64), depth=6, width=5120, classes=200, keep=0.9, batch=512, eps=1 / 255),
+    4: dict(label="configs[4]: SortNet-MLP-2x (5 x 10240 + head 1000), input [1024, 12288] sharded 128 per GPU over 8, "
+                  "keep 0.9, eps 1/255",
+            input_dim=(3, 64, 64), depth=6, width=10240, classes=1000, keep=0.9, batch=128, eps=1 / 255),
+}
+HEADLINE = CONFIGS[1]
+ADAM = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (bound_fwd_tma_kernel_512x5120x5120.md; inf_fwd_sk_kernel_masked_512x4619x4596.md,
-# forward + resolve kernels), at the shapes of the widest layers of this workload.
+# forward + resolve kernels), at the shapes of the widest layers of the headline workload.
 NCU_DRAM_BYTES_PER_LAUNCH = {
     "snb_bound_inf_dist_forward_nograd": 202.7e6,
     "snb_inf_dist_forward_ws": 262.2e6,
 }
 
 
-def layer_dims():
-    pixels = WORKLOAD["input_dim"][0] * WORKLOAD["input_dim"][1] * WORKLOAD["input_dim"][2]
-    w = WORKLOAD["width"]
-    return [(pixels, w)] + [(w, w)] * (WORKLOAD["depth"] - 2) + [(w, WORKLOAD["classes"])]
+def layer_dims(cfg):
+    pixels = cfg["input_dim"][0] * cfg["input_dim"][1] * cfg["input_dim"][2]
+    w = cfg["width"]
+    return [(pixels, w)] + [(w, w)] * (cfg["depth"] - 2) + [(w, cfg["classes"])]
 
 
 # ------------------------------------------------------------------------------------------
-# CPU arm: the reference's PyTorch formulation (restated), on a bounded slice of the workload
+# CPU arm: the reference's own PyTorch branches (or their restatement) on a bounded slice
 # ------------------------------------------------------------------------------------------
 
-def cpu_step_seconds(out_slice, threads):
+def cpu_functions():
+    """(functions, kind): the reference's own operator functions when its Python is staged under
+    oracle/_ref/py, else the restatement in oracle/torch_fallback.py."""
+    from oracle import torch_fallback
+    try:
+        fns = torch_fallback.reference_functions()
+    except Exception:
+        fns = None
+    return (fns, "reference") if fns is not None else (None, "port")
+
+
+def cpu_step_seconds(out_slice, threads, fns):
     import torch
     from oracle import torch_fallback
     torch.set_num_threads(threads)
-    scaled, info = torch_fallback.time_training_slice(
-        layer_dims(), WORKLOAD["keep"], WORKLOAD["p"], WORKLOAD["eps_bound"], out_slice=out_slice, rows=32)
-    return scaled, info
+    return torch_fallback.time_training_slice(layer_dims(HEADLINE), HEADLINE["keep"], INF, HEADLINE["eps"],
+                                              out_slice=out_slice, rows=32, functions=fns)
+
+
+CPU_SAMPLE = ("32 rows (one sub-batch) x %d of the kept outputs of every wide layer x all inputs, all 6 layers: masked "
+              "l-inf forward + autograd backward + dense interval-bound forward through %s, on the host; each part "
+              "scaled by outputs_full / outputs_timed; %.2f s of CPU work per step")
+CPU_HOW = {"reference": "the reference's own norm_dist / bound_inf_dist with use_custom_cuda_func=False",
+           "port": "a restatement of the reference's PyTorch branches (its Python is not staged here)"}
 
 
 def run_reference_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     threads = os.cpu_count() or 1
+    fns, kind = cpu_functions()
     out_slice = 128
     for _ in range(max(args.warmup, 1)):
-        cpu_step_seconds(out_slice, threads)
-    t = []
-    raw = []
+        cpu_step_seconds(out_slice, threads, fns)
+    t, raw = [], []
     for _ in range(args.steps):
-        s, info = cpu_step_seconds(out_slice, threads)
+        s, info = cpu_step_seconds(out_slice, threads, fns)
         t.append(s)
         raw.append(info["raw_seconds"])
-    per32 = statistics.mean(t)
-    value = 32.0 / per32
-    sample = ("32 rows (one sub-batch) x %d of the kept outputs of every wide layer x all inputs, all 6 layers, "
-              "masked l-inf fwd + autograd bwd + dense interval-bound fwd; each part scaled by outputs_full / "
-              "outputs_timed; %.2f s of CPU work per step" % (out_slice, statistics.mean(raw)))
+    value = 32.0 / statistics.mean(t)
     line = {
         "impl": "reference", "metric": "train samples/s (fwd+bwd+IBP step)", "value": value, "unit": "samples/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * 512 / value,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_block(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": config_block(args.gpus, None),
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": kind,
+                         "sample": CPU_SAMPLE % (out_slice, CPU_HOW[kind], statistics.mean(raw))},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def config_block(n):
+def config_block(n, exchange):
     return {
-        "workload": "configs[1]: SortNet-MLP (5 x 5120 + head 10), CIFAR-shaped input [512, 3072] per GPU, "
-                    "keep 0.9 sub-batch masks, p = inf, train eps 8/255, IBP eps 8/255",
-        "global_batch": WORKLOAD["batch_per_gpu"] * n, "batch_per_gpu": WORKLOAD["batch_per_gpu"],
+        "workload": HEADLINE["label"],
+        "global_batch": HEADLINE["batch"] * n, "batch_per_gpu": HEADLINE["batch"],
         "parallelism": "dp%d" % n,
-        "optimizer": "AdamW, fused flat-buffer kernel" + (" with the gradient exchange over NVLink peer memory" if n > 1 else ""),
+        "optimizer": "AdamW, fused flat-buffer kernel" + ("; gradient exchange: " + exchange if exchange and n > 1 else ""),
         "l2": "weights alone are 482 MB per step, larger than the 126 MB L2; no explicit flush",
     }
 
@@ -110,7 +140,7 @@ def config_block(n):
 # ------------------------------------------------------------------------------------------
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU through NVML (read only) every 100 ms."""
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only) every 50 ms."""
 
     def __init__(self, index):
         super().__init__(daemon=True)
@@ -150,28 +180,442 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._halt.wait(0.1)
+            self._halt.wait(0.05)
 
     def finish(self):
         self._halt.set()
         if self.is_alive():
             self.join(timeout=2)
         med = statistics.median(self.samples) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
 def mixture_loss(logits, margin, targets, lam=0.1, clip=1.0):
+    """The reference's `mixture` loss (main.py:357-364): clipped worst-case margin + lam * cross-entropy."""
     import torch.nn.functional as F
     res = margin.clamp(min=0, max=clip)
     return res.max(dim=1)[0].mean() + lam * F.cross_entropy(logits, targets)
 
 
+class Job:
+    """One model of one configuration on this rank with its optimiser, synthetic data and step."""
+
+    def __init__(self, cfg, dev, world, rank, exchange="none", batch=None, seed=0):
+        import torch
+        from sortnet_b200 import layers
+        from sortnet_b200.dist import broadcast_parameters
+        from sortnet_b200.optim import FlatAdamW
+        self.cfg, self.dev, self.world, self.rank = cfg, dev, world, rank
+        self.B = batch or cfg["batch"]
+        torch.manual_seed(seed)
+        self.model = layers.SortMLPModel(depth=cfg["depth"], width=cfg["width"], input_dim=cfg["input_dim"],
+                                         num_classes=cfg["classes"], dropout=cfg["keep"]).to(dev)
+        self.model.set_p(INF)
+        if world > 1 and exchange != "none":
+            broadcast_parameters(self.model)
+        torch.manual_seed(1 + rank)  # masks and data differ per rank, like the reference's seed + rank
+        self.exchange = exchange
+        if exchange == "copies":
+            self.opt = FlatAdamW(self.model, peer_memory=True, overlap=True, **ADAM)
+        elif exchange == "fused":
+            self.opt = FlatAdamW(self.model, peer_memory=True, overlap=False, **ADAM)
+        else:                                   # "nccl": one flat all-reduce; "none": local optimiser
+            self.opt = FlatAdamW(self.model, peer_memory=False, **ADAM)
+        pool = 4
+        gen = torch.Generator().manual_seed(100 + rank)
+        self.host_x = [torch.rand(self.B, *cfg["input_dim"], generator=gen).pin_memory() for _ in range(pool)]
+        self.host_t = [torch.randint(0, cfg["classes"], (self.B,), generator=gen).pin_memory() for _ in range(pool)]
+        self.dev_x = [t.to(dev) for t in self.host_x]
+        self.dev_t = [t.to(dev) for t in self.host_t]
+        self.up = torch.ones(1, device=dev)
+        self.down = torch.zeros(1, device=dev)
+        self.pool = pool
+
+    def bound_pass(self, x, t):
+        """The l-inf interval-bound forward of the whole net (point value + bounds, running means
+        subtracted, certified fraction): the plain l-inf distance in every layer, see
+        SortMLPModel.certified_margin(sort_eval=False)."""
+        import torch
+        with torch.no_grad():
+            return self.model.certified_margin(x, t, self.cfg["eps"], self.up, self.down, sort_eval=False)
+
+    def step(self, x, t, update=True, bounds=True):
+        model, opt = self.model, self.opt
+        model.train()
+        logits, margin = model(x, targets=t, eps=self.cfg["eps"])
+        loss = mixture_loss(logits, margin, t)
+        opt.zero_grad()
+        loss.backward()
+        opt.gather_grads()
+        cert = None
+        if not update:
+            if bounds:
+                cert = self.bound_pass(x, t)
+        elif opt.overlap:
+            opt.begin_exchange()              # side stream: barrier, copies, the shard's update, copies, barrier
+            if bounds:
+                cert = self.bound_pass(x, t)  # reads the pre-update weights
+            opt.end_exchange()
+        else:
+            # same order as the overlapped path: the bound pass reads the pre-update weights
+            if bounds:
+                cert = self.bound_pass(x, t)
+            if self.exchange == "nccl":
+                opt.all_reduce()
+            opt.step()
+        return loss, cert
+
+    def run(self, n, update=True, bounds=True):
+        for i in range(n):
+            self.step(self.dev_x[i % self.pool], self.dev_t[i % self.pool], update=update, bounds=bounds)
+
+    def timed(self, steps, warmup, barrier, **kw):
+        """Device-timed mean milliseconds per step over `steps` steps after `warmup` (this rank)."""
+        import torch
+        self.run(warmup, **kw)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        self.run(steps, **kw)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
+    def release(self):
+        import torch
+        self.model = self.opt = self.dev_x = self.dev_t = self.host_x = self.host_t = None
+        gc.collect()
+        torch.cuda.empty_cache()
+
+
+def max_over_ranks(values, dev, world):
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(values, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def dp_check(job, dev, world):
+    """Correctness of the data-parallel step, outside the timed regions.
+    (i) every rank's flat parameter buffer equals rank 0's, bit for bit;
+    (ii) one more step taken two ways from the same local gradients: the selected exchange, and
+    a plain all-reduce (NCCL) of the gradients followed by the single-GPU fused AdamW kernel on a
+    copy of the parameters with the full moments gathered from the ranks' shards."""
+    import torch
+    import torch.distributed as dist
+    from sortnet_b200 import _lib
+    opt = job.opt
+    opt.check()
+    torch.cuda.synchronize()
+
+    def identical():
+        mine = opt.flat_param.detach().clone()
+        other = mine.clone()
+        dist.broadcast(other, src=0)
+        flag = torch.tensor([1.0 if torch.equal(mine, other) else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item() == 1.0)
+
+    same_before = identical()
+    n = opt.numel
+    p0 = opt.flat_param.detach().clone()
+    g_sum = opt.flat_grad.detach().clone()
+    dist.all_reduce(g_sum)
+    if opt.peer:                               # moments are sharded: rebuild the full vectors
+        m_full = torch.zeros(n, device=dev)
+        v_full = torch.zeros(n, device=dev)
+        k = opt.hi - opt.lo
+        m_full[opt.lo:opt.hi] = opt.exp_avg[:k]
+        v_full[opt.lo:opt.hi] = opt.exp_avg_sq[:k]
+        dist.all_reduce(m_full)
+        dist.all_reduce(v_full)
+    else:
+        m_full, v_full = opt.exp_avg.clone(), opt.exp_avg_sq.clone()
+    rc = _lib.load().snb_adamw_step(p0.data_ptr(), g_sum.data_ptr(), m_full.data_ptr(), v_full.data_ptr(), n,
+                                    ADAM["lr"], ADAM["betas"][0], ADAM["betas"][1], ADAM["eps"], ADAM["weight_decay"],
+                                    opt.step_count + 1, 1.0 / world, torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "adamw_step")
+    # the selected exchange on the very same local gradients (mark them as this step's)
+    for prm in opt.params:
+        prm.grad_sink_written = True
+    if job.exchange == "nccl":
+        opt.all_reduce()
+    opt.step()
+    torch.cuda.synchronize()
+    opt.check()
+    diff = (opt.flat_param - p0).abs().max()
+    scale = p0.abs().max().clamp(min=1.0)
+    worst = torch.stack([diff / scale])
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    same_after = identical()
+    ok = same_before and same_after and float(worst) <= 1e-5
+    return {"replicas_identical": same_before and same_after, "max_rel_vs_allreduce": float(worst),
+            "tolerance": 1e-5, "exchange": job.exchange, "ok": ok}
+
+
+def fp32_peak_gflops(dev):
+    """FP32 CUDA-core peak of this GPU, measured now with a register-only FMA chain (2 flops per FMA)."""
+    import torch
+    from sortnet_b200 import _lib
+    scratch = torch.zeros(4, device=dev)
+    lib = _lib.load()
+    flops = ctypes.c_double()
+    best = 0.0
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _lib.check(lib.snb_probe_fp32(scratch.data_ptr(), 4096, ctypes.byref(flops),
+                                      torch.cuda.current_stream().cuda_stream), "probe_fp32")
+        b.record()
+        torch.cuda.synchronize()
+        best = max(best, flops.value / (a.elapsed_time(b) * 1e-3))
+    return best * 1e-9
+
+
+PEAK_SOURCE = ("FFMA probe timed in this run (2 flops per FMA); MEASURED_PEAKS.json has no FP32 figure; nominal "
+               "148 SM x 128 lanes x 2 x 1.965 GHz = 74.5 TFLOP/s")
+
+
+def kernel_stats(timeline, entry):
+    """Launches of `entry` on the widest layers (mask sizes differ a little from step to step, so
+    every shape within 10 % of the largest counts): a representative shape, the mean time per
+    launch and the mean element count per launch."""
+    rows = {k[1]: v for k, v in timeline.items() if k[0] == entry}
+    if not rows:
+        return None
+    size = lambda t: t[0] * t[1] * t[2]
+    biggest = max(size(t) for t in rows)
+    picked = {t: v for t, v in rows.items() if size(t) >= 0.9 * biggest}
+    launches = sum(len(v) for v in picked.values())
+    total_ms = sum(sum(v) for v in picked.values())
+    elems = sum(size(t) * len(v) for t, v in picked.items()) / launches
+    return max(picked, key=size), total_ms / launches, elems
+
+
+def profiled_pass(job, steps, **kw):
+    """A few steps with a CUDA-event pair around every entry-point call: {(entry, shape): [ms]}."""
+    from sortnet_b200 import norm_dist_cuda as C
+    C.start_profile()
+    job.run(steps, **kw)
+    return C.stop_profile()
+
+
+def roofline_blocks(timeline, peak_gflops):
+    by_entry = {}
+    for (entry, tag), v in timeline.items():
+        by_entry[entry] = by_entry.get(entry, 0.0) + sum(v)
+    total = sum(by_entry.values())
+    shares = {k[4:]: round(v / total, 4) for k, v in sorted(by_entry.items(), key=lambda kv: -kv[1])}
+    roofs = {}
+    for entry, ops_per_elem in (("snb_bound_inf_dist_forward_nograd", 6.0), ("snb_inf_dist_forward_ws", 2.0),
+                                ("snb_inf_dist_forward_nograd", 2.0)):
+        ks = kernel_stats(timeline, entry)
+        if ks is None:
+            continue
+        (b_, co_, ci_), mean_ms, mean_elems = ks
+        achieved = ops_per_elem * mean_elems / (mean_ms * 1e-3) * 1e-9
+        roofs[entry] = {
+            "bound": "fp32", "kernel": entry[4:], "shape_B_CO_CI": [b_, co_, ci_],
+            "ops_per_element": ops_per_elem, "ms_per_launch": round(mean_ms, 4),
+            "achieved": round(achieved, 1), "peak": round(peak_gflops, 1), "unit": "GFLOP/s",
+            "frac": round(achieved / peak_gflops, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(entry),
+            "peak_source": PEAK_SOURCE,
+        }
+    dominant = max(roofs.values(), key=lambda r: by_entry.get("snb_" + r["kernel"], 0.0)) if roofs else None
+    return shares, roofs, dominant, total
+
+
+def lp_blocks(job, peak_gflops, sm_mhz):
+    """The p-annealed phases of the recipe (p = 8, then a general p) on the headline model: one masked
+    training step without the bound pass, device-timed over 10 steps, plus the generic-p kernels
+    against the special-function-unit roof (2 transcendentals per element; 16 per clock per SM)."""
+    import torch
+    out, roof = {}, None
+    for p_val in (8.0, 31.6):
+        job.model.set_p(p_val)
+        ms = job.timed(10, 2, torch.cuda.synchronize, bounds=False)
+        out["p=%g" % p_val] = {"ms_per_step": round(ms, 3), "samples_per_s": round(job.B / (ms * 1e-3), 1), "steps": 10}
+        if p_val == 31.6:
+            tl = profiled_pass(job, 2, bounds=False)
+            sms = torch.cuda.get_device_properties(job.dev).multi_processor_count
+            xu_peak = 16.0 * sms * (sm_mhz or 1965.0) * 1e6 * 1e-9          # G transcendentals / s
+            roof = {"bound": "xu (special-function unit)", "peak": round(xu_peak, 1), "unit": "G transcendental/s",
+                    "peak_source": "16 per clock per SM x %d SMs x %s MHz (median SM clock of this run)" % (sms, sm_mhz),
+                    "ops_per_element": 2.0, "p": 31.6}
+            for entry, key in (("snb_norm_dist_forward_ws", "forward"), ("snb_norm_dist_backward_input_weight", "backward")):
+                ks = kernel_stats(tl, entry)
+                if ks is None:
+                    continue
+                shape, mean_ms, elems = ks
+                ach = 2.0 * elems / (mean_ms * 1e-3) * 1e-9
+                roof[key] = {"shape_B_CO_CI": list(shape), "ms_per_launch": round(mean_ms, 4),
+                             "achieved": round(ach, 1), "frac": round(ach / xu_peak, 4)}
+            roof["note"] = "the forward's time includes the l-inf pass that supplies the normaliser and the root kernel"
+    job.model.set_p(INF)
+    return out, roof
+
+
+def hbm_block(job):
+    """The HBM-bound kernel of the step (fused AdamW: 4 reads + 3 writes of 4 bytes per parameter)
+    against the measured copy bandwidth of this pool's B200s."""
+    import torch
+    opt = job.opt
+    hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm_peak = float(json.load(f)["hbm_gbs"])
+            hbm_src = "MEASURED_PEAKS.json hbm_gbs (STREAM-style copy)"
+    except Exception:
+        pass
+    a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    opt.step()
+    torch.cuda.synchronize()
+    a_ev.record()
+    for _ in range(5):
+        opt.step()
+    b_ev.record()
+    torch.cuda.synchronize()
+    adam_ms = a_ev.elapsed_time(b_ev) / 5
+    adam_gbs = 28.0 * opt.numel / (adam_ms * 1e-3) * 1e-9
+    return {"bound": "hbm", "kernel": "adamw_kernel", "ms_per_launch": round(adam_ms, 4),
+            "achieved": round(adam_gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(adam_gbs / hbm_peak, 4),
+            "traffic": None, "algorithmic_bytes": 28 * opt.numel, "peak_source": hbm_src}
+
+
+def single_layer_block(dev, peak_gflops):
+    """configs[0]: one l-inf layer, x [128, 784], W [5120, 784], box [x - 0.3, x + 0.3] clipped to
+    [0, 1]: forward with argmax words, sparse backward, interval bounds, each device-timed.  The
+    weights rotate through 9 copies (145 MB) so that no launch finds its operands in L2."""
+    import torch
+    from sortnet_b200 import norm_dist_cuda as C
+    B, CI, CO = 128, 784, 5120
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.rand(B, CI, 1, device=dev, generator=g)
+    ws = [torch.randn(CO, CI, device=dev, generator=g) for _ in range(9)]
+    xl, xu = (x - 0.3).clamp(0, 1), (x + 0.3).clamp(0, 1)
+    gy = torch.randn(B, CO, 1, device=dev, generator=g)
+    y, pos = torch.empty(B, CO, 1, device=dev), torch.empty(B, CO, 1, device=dev, dtype=torch.int32)
+    yl, yu = torch.empty_like(y), torch.empty_like(y)
+    gx, gw = torch.empty_like(x), torch.empty_like(ws[0])
+
+    def timed(fn, iters=27):
+        for i in range(3):
+            fn(ws[i % 9])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters):
+            fn(ws[i % 9])
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
+    E = B * CI * CO
+    t_f = timed(lambda w: C.inf_dist_forward(x, w, y, pos, 1))
+    t_b = timed(lambda w: C.inf_dist_backward_input_weight(gy, pos, gx, gw, 1))
+    t_i = timed(lambda w: C.bound_inf_dist_forward_nograd(xl, xu, w, yl, yu, 1))
+    frac = lambda ops, ms: round(ops * E / (ms * 1e-3) * 1e-9 / peak_gflops, 4)
+    bwd_bytes = 8 * B * CO + 4 * B * CI + 4 * CO * CI      # g + pos read, grad_x written, grad_w zero-filled
+    return {"workload": "configs[0]: single l-inf layer 128 x 784 -> 5120, fwd + argmax, sparse bwd, interval bounds",
+            "forward_ms": round(t_f, 4), "forward_frac_fp32": frac(2.0, t_f),
+            "backward_ms": round(t_b, 4), "backward_gbs": round(bwd_bytes / (t_b * 1e-3) * 1e-9, 1),
+            "bounds_ms": round(t_i, 4), "bounds_frac_fp32": frac(6.0, t_i),
+            "samples_per_s": round(B / ((t_f + t_b + t_i) * 1e-3), 1), "l2": "weights rotate through 145 MB"}
+
+
+def config_step_block(idx, dev, steps=10, warmup=3):
+    """A secondary configuration at N = 1: the same step definition as the headline."""
+    import torch
+    cfg = CONFIGS[idx]
+    job = Job(cfg, dev, 1, 0, exchange="none")
+    ms = job.timed(steps, warmup, torch.cuda.synchronize)
+    out = {"workload": cfg["label"], "ms_per_step": round(ms, 3), "samples_per_s": round(job.B / (ms * 1e-3), 1),
+           "steps": steps}
+    job.release()
+    return out
+
+
+def gpu_comparator_block(job, steps=10, warmup=3):
+    """The headline step through the reference itself on this GPU: its unmodified SortMLPModel and
+    operator layer (staged under oracle/_ref/py) over its own CUDA extension compiled for sm_100a
+    (oracle/_ref/norm_dist_cuda.so), torch.optim.AdamW, same weights, same data.  The bound pass is
+    the reference's own keep-rate-1 path (norm_dist no-grad + bound_inf_dist per layer, running
+    means subtracted), i.e. the work the headline step does.  `eval_faithful_bound_pass` times, for
+    both sides, the evaluation forward the reference's certified_test really runs on this model
+    (sort neuron + its bounds, K = 10)."""
+    import torch
+    from oracle import build_ref
+    ext = build_ref.load()
+    if ext is None or build_ref.staged_python() is None:
+        return {"unavailable": "oracle/_ref holds no build of the reference (no reference checkout on the build machine)"}
+    cfg, dev = job.cfg, job.dev
+    ref_ops, ref_models, ref_nets = build_ref.import_reference_python(ext)
+    ref_models.NormDistBase.dropout_list.clear()
+    ref_models.NormDistBase.dropout_buffer = None
+    torch.manual_seed(0)
+    model = ref_nets.SortMLPModel(depth=cfg["depth"], width=cfg["width"], input_dim=cfg["input_dim"],
+                                  num_classes=cfg["classes"], dropout=cfg["keep"]).to(dev)
+    model.load_state_dict(job.model.state_dict())
+    opt = torch.optim.AdamW(model.parameters(), **ADAM)
+    eps = cfg["eps"]
+    drop_list = ref_models.NormDistBase.dropout_list
+
+    def bound_pass(x, t, faithful):
+        model.eval()
+        saved = dict(drop_list)
+        if not faithful:
+            drop_list.clear()                 # the reference's own branch for layers without a keep rate
+        try:
+            with torch.no_grad():
+                _, margin = model(x, targets=t, eps=eps, up=job.up, down=job.down)
+        finally:
+            drop_list.clear()
+            drop_list.update(saved)
+        return (margin.scatter(1, t.view(-1, 1), float("-inf")).max(dim=1)[0] < 0).float().mean()
+
+    def step(x, t):
+        model.train()
+        logits, margin = model(x, targets=t, eps=eps)
+        loss = mixture_loss(logits, margin, t)
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        cert = bound_pass(x, t, False)
+        opt.step()
+        return loss, cert
+
+    def timed(fn, n, w):
+        for i in range(w):
+            fn(job.dev_x[i % job.pool], job.dev_t[i % job.pool])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            fn(job.dev_x[i % job.pool], job.dev_t[i % job.pool])
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    ms_ref = timed(step, steps, warmup)
+    ms_ref_faithful = timed(lambda x, t: bound_pass(x, t, True), 3, 1)
+    with torch.no_grad():
+        ms_ours_faithful = timed(lambda x, t: job.model.certified_margin(x, t, eps, job.up, job.down), 3, 1)
+    del model, opt
+    gc.collect()
+    torch.cuda.empty_cache()
+    return {"what": "configs[1] step through the reference's SortMLPModel + core/norm_dist.py over its own CUDA "
+                    "extension built for sm_100a, torch.optim.AdamW, l-inf bound pass via its keep-rate-1 branch",
+            "ms_per_step": round(ms_ref, 3), "samples_per_s": round(job.B / (ms_ref * 1e-3), 1), "steps": steps,
+            "eval_faithful_bound_pass": {"what": "evaluation forward with the sort neuron and its bounds (K = 10), no grad",
+                                         "reference_ms": round(ms_ref_faithful, 3), "ours_ms": round(ms_ours_faithful, 3),
+                                         "speedup": round(ms_ref_faithful / ms_ours_faithful, 3)}}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
-    from sortnet_b200 import _lib, layers, norm_dist_cuda as C
-    from sortnet_b200.dist import broadcast_parameters
-    from sortnet_b200.optim import FlatAdamW
+    from sortnet_b200 import _lib, norm_dist_cuda as C
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
@@ -187,137 +631,66 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # stdout carries the one JSON line: NCCL's own log lines (its version banner, anything
-        # NCCL_DEBUG asks for) go to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        # SNB_NCCL_MAX_CTAS > 0 caps the CTAs NCCL may use.  Measured at N = 8: 2 / 4 / 8 CTAs give
-        # 31.1 / 29.3 / 28.5 ms per step, NCCL's own choice 27.2 ms, so the default is no cap.
-        opts = dist.ProcessGroupNCCL.Options()
-        max_ctas = int(os.environ.get("SNB_NCCL_MAX_CTAS", "0"))
-        if max_ctas > 0:
-            opts.config.max_ctas = max_ctas
-            opts.config.min_ctas = min(max_ctas, 4)
-        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+        dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
-    B = WORKLOAD["batch_per_gpu"]
-    torch.manual_seed(0)
-    model = layers.SortMLPModel(depth=WORKLOAD["depth"], width=WORKLOAD["width"], input_dim=WORKLOAD["input_dim"],
-                                num_classes=WORKLOAD["classes"], dropout=WORKLOAD["keep"]).to(dev)
-    model.set_p(WORKLOAD["p"])
-    broadcast_parameters(model)
-    torch.manual_seed(1 + rank)  # masks and data differ per rank, like the reference's seed + rank
-    # parameters, gradients and AdamW moments in flat buffers: one all-reduce, one fused update,
-    # weight gradients written in place by the backward kernels
     # N > 1: the gradient exchange runs as device-to-device copies over NVLink on a side stream,
     # beside the bound pass, with a local sum + AdamW kernel for this rank's shard in between
-    # (SNB_COPY_EXCHANGE=0: one fused kernel over peer memory, not overlapped; SNB_PEER_STEP=0: one
-    # NCCL all-reduce followed by the local fused AdamW)
-    peer_step = world > 1 and os.environ.get("SNB_PEER_STEP", "1") != "0"
-    adam = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
-    exchange = "none (single GPU)"
-    if peer_step:
-        try:
-            # the copy-based exchange has been run and checked on 2 GPUs only (no larger box was
-            # free when it was written), so it is the default there; larger worlds keep the fused
-            # kernel, which has been measured at N = 4 and 8, unless SNB_COPY_EXCHANGE=1 asks for it
-            copy_exchange = os.environ.get("SNB_COPY_EXCHANGE", "1" if world == 2 else "0") != "0"
-            opt = FlatAdamW(model, peer_memory=True, overlap=copy_exchange, **adam)
-            exchange = ("device-to-device copies over NVLink (reduce-scatter, all-gather) + local sum/AdamW kernel, "
-                        "all beside the bound pass" if copy_exchange else
-                        "fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory")
-        except Exception as exc:                          # symmetric memory not available: use NCCL
-            if rank == 0:
-                print("peer-memory step unavailable (%s); using one NCCL all-reduce" % exc, file=sys.stderr)
-            peer_step = False
-    if not peer_step:
-        opt = FlatAdamW(model, peer_memory=False, **adam)
-        if world > 1:
-            exchange = "one flat NCCL all-reduce + local fused AdamW"
-    # every rank must have taken the same path
+    # ("copies"); "fused" = one kernel doing reduce-scatter + AdamW + all-gather over peer pointers,
+    # not overlapped; "nccl" = one flat all-reduce followed by the local fused AdamW.
+    exchange = "none"
     if world > 1:
-        flag = torch.tensor([1.0 if peer_step else 0.0], device=dev)
+        exchange = args.exchange
+        if exchange != "nccl":
+            try:
+                job = Job(HEADLINE, dev, world, rank, exchange=exchange)
+            except Exception as exc:                      # symmetric memory not available: use NCCL
+                print("rank %d: peer-memory step unavailable (%s); using one NCCL all-reduce" % (rank, exc), file=sys.stderr)
+                exchange = "nccl"
+        flag = torch.tensor([1.0 if exchange == "nccl" else 0.0], device=dev)
         dist.all_reduce(flag)
         if 0.0 < float(flag) < world:
             raise SystemExit("ranks disagree on the gradient-exchange path")
-
-    pool = 4
-    gen = torch.Generator().manual_seed(100 + rank)
-    host_x = [torch.rand(B, *WORKLOAD["input_dim"], generator=gen).pin_memory() for _ in range(pool)]
-    host_t = [torch.randint(0, WORKLOAD["classes"], (B,), generator=gen).pin_memory() for _ in range(pool)]
-    dev_x = [t.to(dev) for t in host_x]
-    dev_t = [t.to(dev) for t in host_t]
-    up = torch.ones(1, device=dev)
-    down = torch.zeros(1, device=dev)
-    eps_t, eps_b = WORKLOAD["eps_train"], WORKLOAD["eps_bound"]
-
-    overlap_bounds = os.environ.get("SNB_OVERLAP_BOUNDS", "0") != "0"
-
-    def step(x, t):
-        model.train()
-        logits, margin = model(x, targets=t, eps=eps_t)
-        loss = mixture_loss(logits, margin, t)
-        opt.zero_grad()
-        loss.backward()
-        opt.gather_grads()
-        if opt.overlap:
-            opt.begin_exchange()                          # side stream: copies + the shard's update
-            with torch.no_grad():
-                cert = model.certified_margin(x, t, eps_b, up, down)   # reads the pre-update weights
-            opt.end_exchange()
-        elif overlap_bounds:
-            work = opt.all_reduce(async_op=True)          # certification pass overlaps the exchange
-            with torch.no_grad():
-                cert = model.certified_margin(x, t, eps_b, up, down)
-            if work is not None:
-                work.wait()
-            opt.step()
-        else:
-            # Measured at N = 8: hiding an NCCL exchange behind the bound kernels costs more than it
-            # saves (NCCL's CTAs hold SMs that the one-wave compute kernels are sized for:
-            # 27.8 ms per step overlapped, 26.0 ms exposed), so the exchange is not overlapped: it
-            # is part of step() (peer-memory kernel) or one flat all-reduce right before it.
-            # Same order as the overlapped path: the bound pass reads the pre-update weights.
-            with torch.no_grad():
-                cert = model.certified_margin(x, t, eps_b, up, down)
-            opt.all_reduce()
-            opt.step()
-        return loss, cert
+    if exchange in ("none", "nccl"):
+        job = Job(HEADLINE, dev, world, rank, exchange=exchange)
+    exchange_text = {
+        "none": "none (single GPU)",
+        "copies": "device-to-device copies over NVLink (reduce-scatter, all-gather) + local sum/AdamW kernel, all beside "
+                  "the bound pass, ordered by bounded peer barriers",
+        "fused": "fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory",
+        "nccl": "one flat NCCL all-reduce + local fused AdamW"}[exchange]
+    B = job.B
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(dev_x[i % pool], dev_t[i % pool])
+    job.run(args.warmup)
     barrier()
 
-    # ---- timed region 1: inputs resident in HBM ------------------------------------------
+    # ---- timed region 1: inputs resident in HBM, no per-call events ---------------------
     sampler = ClockSampler(local)
     sampler.start()
     C.reset_counters()
-    C.start_profile()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for i in range(args.steps):
-        step(dev_x[i % pool], dev_t[i % pool])
+    job.run(args.steps)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
     launches = C.launch_count
-    timeline = C.stop_profile()
-    clocks = sampler.finish()
+    job.opt.check()
 
     # ---- timed region 2: end to end from pinned host memory ------------------------------
-    import gc
-    warm_x, warm_t = torch.empty_like(dev_x[0]), torch.empty_like(dev_t[0])
+    warm_x, warm_t = torch.empty_like(job.dev_x[0]), torch.empty_like(job.dev_t[0])
     warm_out = torch.zeros(2, pin_memory=True)
     for i in range(2):                                     # first use of the copy paths, untimed
-        warm_x.copy_(host_x[i % pool], non_blocking=True)
-        warm_t.copy_(host_t[i % pool], non_blocking=True)
-        loss, cert = step(warm_x, warm_t)
+        warm_x.copy_(job.host_x[i % job.pool], non_blocking=True)
+        warm_t.copy_(job.host_t[i % job.pool], non_blocking=True)
+        loss, cert = job.step(warm_x, warm_t)
         warm_out[0].copy_(loss.detach(), non_blocking=True)
         warm_out[1].copy_(cert, non_blocking=True)
     gc.collect()
@@ -330,16 +703,16 @@ def run_gpu_arm(args):
     # it never waits for the step it has just enqueued.  All copies and reads are inside the
     # timed region.
     main_stream = torch.cuda.current_stream(dev)
-    in_x = [torch.empty_like(dev_x[0]) for _ in range(2)]
-    in_t = [torch.empty_like(dev_t[0]) for _ in range(2)]
+    in_x = [torch.empty_like(job.dev_x[0]) for _ in range(2)]
+    in_t = [torch.empty_like(job.dev_t[0]) for _ in range(2)]
     results = torch.zeros(args.steps, 2, pin_memory=True)
     sink = 0.0
     done = []
     for i in range(args.steps):
         x, t = in_x[i % 2], in_t[i % 2]
-        x.copy_(host_x[i % pool], non_blocking=True)
-        t.copy_(host_t[i % pool], non_blocking=True)
-        loss, cert = step(x, t)
+        x.copy_(job.host_x[i % job.pool], non_blocking=True)
+        t.copy_(job.host_t[i % job.pool], non_blocking=True)
+        loss, cert = job.step(x, t)
         results[i, 0].copy_(loss.detach(), non_blocking=True)
         results[i, 1].copy_(cert, non_blocking=True)
         ev = torch.cuda.Event()
@@ -353,154 +726,130 @@ def run_gpu_arm(args):
     e3.record()
     barrier()
     gc.enable()
+    clocks = sampler.finish()
     ms_e2e = e2.elapsed_time(e3) / args.steps
+    job.opt.check()
+    if not math.isfinite(sink):
+        raise SystemExit("the step produced a non-finite loss")
+    ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev, world)
 
-    times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    # ---- a short separate pass with an event pair around every entry-point call ---------
+    timeline = profiled_pass(job, 3)
+    barrier()
+    peak_gflops = fp32_peak_gflops(dev) if rank == 0 else None
+
+    extra = {}
+    failed = False
     if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = float(times[0]), float(times[1])
+        extra["dp_check"] = dp_check(job, dev, world)
+        failed = not extra["dp_check"]["ok"]
+        # what the exchange leaves exposed: the same step without exchange and update
+        ms_compute = job.timed(5, 1, barrier, update=False)
+        (ms_compute,) = max_over_ranks([ms_compute], dev, world)
+        extra["exchange_ms_exposed"] = round(ms - ms_compute, 3)
+        # strong scaling: the global batch of the single-GPU run (512) split over the ranks
+        if HEADLINE["batch"] % (32 * world) == 0:
+            sub = HEADLINE["batch"] // world
+            small = [(x[:sub].contiguous(), t[:sub].contiguous()) for x, t in zip(job.dev_x, job.dev_t)]
 
+            def strong(n, **kw):
+                for i in range(n):
+                    job.step(*small[i % job.pool], **kw)
+
+            def timed_strong(**kw):
+                strong(3, **kw)
+                barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                strong(args.steps, **kw)
+                b.record()
+                barrier()
+                return a.elapsed_time(b) / args.steps
+
+            ms_strong, ms_strong_compute = max_over_ranks([timed_strong(), timed_strong(update=False)], dev, world)
+            # the single-GPU step on the whole batch, timed here on every rank without any exchange
+            # (full local AdamW on a private copy of the model), slowest rank
+            solo = Job(HEADLINE, dev, world, rank, exchange="none")
+            (ms_solo,) = max_over_ranks([solo.timed(5, 3, barrier)], dev, world)
+            solo.release()
+            extra["strong_scaling"] = {
+                "global_batch": HEADLINE["batch"], "batch_per_gpu": sub, "ms_per_step": round(ms_strong, 3),
+                "samples_per_s": round(HEADLINE["batch"] / (ms_strong * 1e-3), 1),
+                "n1_ms_per_step_same_run": round(ms_solo, 3),
+                "efficiency_vs_n1": round(ms_solo / (world * ms_strong), 4),
+                "exchange_ms_exposed": round(ms_strong - ms_strong_compute, 3)}
+            job.opt.check()
+    if world == 8 and not args.no_extras:
+        job.release()
+        cfg = CONFIGS[4]
+        big = Job(cfg, dev, world, rank, exchange=exchange)
+        ms_big = big.timed(10, 3, barrier)
+        ms_big_compute = big.timed(5, 1, barrier, update=False)
+        ms_big, ms_big_compute = max_over_ranks([ms_big, ms_big_compute], dev, world)
+        chk = dp_check(big, dev, world)
+        failed = failed or not chk["ok"]
+        extra["configs[4]"] = {"workload": cfg["label"], "global_batch": cfg["batch"] * world, "batch_per_gpu": cfg["batch"],
+                               "parameters": big.opt.numel, "ms_per_step": round(ms_big, 3),
+                               "samples_per_s": round(cfg["batch"] * world / (ms_big * 1e-3), 1),
+                               "exchange_ms_exposed": round(ms_big - ms_big_compute, 3), "dp_check": chk}
+        big.release()
+
+    line = None
     if rank == 0:
-        # FP32 CUDA-core peak of this GPU, measured now (2 flops per FMA)
-        scratch = torch.zeros(4, device=dev)
-        lib = _lib.load()
-        import ctypes
-        flops = ctypes.c_double()
-        best = 0.0
-        for _ in range(5):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            _lib.check(lib.snb_probe_fp32(scratch.data_ptr(), 4096, ctypes.byref(flops),
-                                          torch.cuda.current_stream().cuda_stream), "probe_fp32")
-            b.record()
-            torch.cuda.synchronize()
-            best = max(best, flops.value / (a.elapsed_time(b) * 1e-3))
-        peak_gflops = best * 1e-9
-
-        def kernel_stats(entry):
-            """Launches of `entry` on the widest layers (mask sizes differ a little from step to
-            step, so every shape within 10 % of the largest counts): a representative shape, the
-            mean time per launch and the mean element count per launch."""
-            rows = {k[1]: v for k, v in timeline.items() if k[0] == entry}
-            if not rows:
-                return None
-            size = lambda t: t[0] * t[1] * t[2]
-            biggest = max(size(t) for t in rows)
-            picked = {t: v for t, v in rows.items() if size(t) >= 0.9 * biggest}
-            launches = sum(len(v) for v in picked.values())
-            total_ms = sum(sum(v) for v in picked.values())
-            elems = sum(size(t) * len(v) for t, v in picked.items()) / launches
-            return max(picked, key=size), total_ms / launches, elems
-
-        by_entry = {}
-        for (entry, tag), v in timeline.items():
-            by_entry[entry] = by_entry.get(entry, 0.0) + sum(v)
-        total_kernel_ms = sum(by_entry.values())
-        shares = {k[4:]: round(v / total_kernel_ms, 4) for k, v in sorted(by_entry.items(), key=lambda kv: -kv[1])}
-
-        roofs = {}
-        for entry, ops_per_elem in (("snb_bound_inf_dist_forward_nograd", 6.0), ("snb_inf_dist_forward_ws", 2.0)):
-            ks = kernel_stats(entry)
-            if ks is None:
-                continue
-            (b_, co_, ci_), mean_ms, mean_elems = ks
-            achieved = ops_per_elem * mean_elems / (mean_ms * 1e-3) * 1e-9
-            roofs[entry] = {
-                "bound": "fp32", "kernel": entry[4:], "shape_B_CO_CI": [b_, co_, ci_],
-                "ops_per_element": ops_per_elem, "ms_per_launch": round(mean_ms, 4),
-                "achieved": round(achieved, 1), "peak": round(peak_gflops, 1), "unit": "GFLOP/s",
-                "frac": round(achieved / peak_gflops, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(entry),
-                "peak_source": "FFMA probe timed in this run (2 flops per FMA); MEASURED_PEAKS.json has no FP32 "
-                               "figure; nominal 148 SM x 128 lanes x 2 x 1.965 GHz = 74.5 TFLOP/s",
-            }
-        dominant = max(roofs.values(), key=lambda r: by_entry.get("snb_" + r["kernel"], 0.0)) if roofs else None
-
         value = world * B / (ms * 1e-3)
         e2e = world * B / (ms_e2e * 1e-3)
-        h2d = sum(t.numel() * t.element_size() for t in (host_x[0], host_t[0]))
+        h2d = sum(t.numel() * t.element_size() for t in (in_x[0], in_t[0]))
         line = {
             "metric": "train samples/s (fwd+bwd+IBP step)", "value": round(value, 1), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_block(world),
+            "config": config_block(world, exchange_text),
             "e2e": {"value": round(e2e, 1), "unit": "samples/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},
             "gpu_launches": launches,
-            "gradient_exchange": exchange,
+            "gradient_exchange": exchange_text,
             "clocks": clocks,
-            "roofline": dominant,
-            "roofline_linf_forward": roofs.get("snb_inf_dist_forward_ws"),
-            "kernel_time_share": shares,
-            "kernel_ms_per_step": round(total_kernel_ms / args.steps, 3),
         }
-        if world == 1 and not args.no_lp:
-            # the p-annealed phases of the recipe (p = 8, then a general p) on the same model: one
-            # masked training step without the bound pass, device-timed, reported beside the headline
-            lp = {}
-            for p_val in (8.0, 31.6):
-                model.set_p(p_val)
-
-                def lp_step(x, t):
-                    model.train()
-                    logits, margin = model(x, targets=t, eps=eps_t)
-                    loss = mixture_loss(logits, margin, t)
-                    opt.zero_grad()
-                    loss.backward()
-                    opt.gather_grads()
-                    opt.step()
-
-                for i in range(2):
-                    lp_step(dev_x[i % pool], dev_t[i % pool])
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                n_lp = 4
-                for i in range(n_lp):
-                    lp_step(dev_x[i % pool], dev_t[i % pool])
-                b.record()
-                torch.cuda.synchronize()
-                t_ms = a.elapsed_time(b) / n_lp
-                lp["p=%g" % p_val] = {"ms_per_step": round(t_ms, 3), "samples_per_s": round(B / (t_ms * 1e-3), 1)}
-            model.set_p(WORKLOAD["p"])
+        if timeline:
+            shares, roofs, dominant, total_kernel_ms = roofline_blocks(timeline, peak_gflops)
+            line.update({"roofline": dominant, "roofline_linf_forward": roofs.get("snb_inf_dist_forward_ws"),
+                         "roofline_linf_point_forward": roofs.get("snb_inf_dist_forward_nograd"),
+                         "kernel_time_share": shares, "kernel_ms_per_step": round(total_kernel_ms / 3, 3),
+                         "kernel_time_source": "3 extra steps with a CUDA-event pair around every entry-point call; the "
+                                               "headline regions run without them"})
+        line.update(extra)
+        if world == 1 and not args.no_extras:
+            line["roofline_hbm"] = hbm_block(job)
+            lp, lp_roof = lp_blocks(job, peak_gflops, clocks.get("sm_mhz"))
             line["lp_training_step"] = lp
-        if world == 1:
-            # the HBM-bound kernel of the step (fused AdamW: 4 reads + 3 writes of 4 bytes per parameter)
-            # against the measured copy bandwidth of this pool's B200s
-            hbm_peak, hbm_src = 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+            if lp_roof:
+                line["roofline_lp"] = lp_roof
             try:
-                with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
-                    hbm_peak = float(json.load(f)["hbm_gbs"])
-                    hbm_src = "MEASURED_PEAKS.json hbm_gbs (STREAM-style copy)"
-            except Exception:
-                pass
-            a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            opt.step()
-            torch.cuda.synchronize()
-            a_ev.record()
-            for _ in range(5):
-                opt.step()
-            b_ev.record()
-            torch.cuda.synchronize()
-            adam_ms = a_ev.elapsed_time(b_ev) / 5
-            adam_gbs = 28.0 * opt.numel / (adam_ms * 1e-3) * 1e-9
-            line["roofline_hbm"] = {"bound": "hbm", "kernel": "adamw_kernel", "ms_per_launch": round(adam_ms, 4),
-                                    "achieved": round(adam_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
-                                    "frac": round(adam_gbs / hbm_peak, 4), "traffic": None,
-                                    "algorithmic_bytes": 28 * opt.numel, "peak_source": hbm_src}
+                cmp_block = gpu_comparator_block(job)
+            except Exception as exc:
+                cmp_block = {"unavailable": "the reference step failed here: %s" % (str(exc).splitlines() or ["?"])[0]}
+            if "ms_per_step" in cmp_block:
+                cmp_block["ours_ms_per_step"] = round(ms, 3)
+                cmp_block["speedup"] = round(cmp_block["ms_per_step"] / ms, 3)
+            line["gpu_comparator"] = cmp_block
+            job.release()
+            line["configs[0]"] = single_layer_block(dev, peak_gflops)
+            line["configs[2]"] = config_step_block(2, dev)
+            line["configs[3]"] = config_step_block(3, dev)
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            cpu_step_seconds(64, threads)                      # warm-up
-            scaled, info = cpu_step_seconds(256, threads)
-            line["cpu_baseline"] = {
-                "value": round(32.0 / scaled, 4), "unit": "samples/s", "cores": threads, "kind": "port",
-                "sample": "32 rows x 256 outputs of every wide layer x all inputs, all 6 layers, masked l-inf "
-                          "fwd + autograd bwd + dense interval-bound fwd in PyTorch on the host (%.1f s), each "
-                          "part scaled by outputs_full / outputs_timed" % info["raw_seconds"],
-            }
+            fns, kind = cpu_functions()
+            cpu_step_seconds(64, threads, fns)                      # warm-up
+            scaled, info = cpu_step_seconds(256, threads, fns)
+            line["cpu_baseline"] = {"value": round(32.0 / scaled, 4), "unit": "samples/s", "cores": threads, "kind": kind,
+                                    "sample": CPU_SAMPLE % (256, CPU_HOW[kind], info["raw_seconds"])}
         sys.stdout.flush()
         os.write(result_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("dp_check failed: the data-parallel step does not match all-reduce + AdamW")
 
 
 def main():
@@ -509,8 +858,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="copies", choices=["copies", "fused", "nccl"],
+                    help="gradient exchange at N > 1 (default: overlapped device-to-device copies)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-lp", action="store_true", help="skip the p = 8 / p = 31.6 training-step extras")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary blocks (other configurations, finite p, "
+                                                              "GPU comparator)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -49,6 +49,7 @@ extern "C" {
 #define SNB_STATUS_CUDA 5
 #define SNB_STATUS_ALIGNMENT 6
 #define SNB_STATUS_STATIC_CAPACITY 7
+#define SNB_STATUS_INDEX_RANGE 8
 
 const char* snb_status_string(int status);
 const char* snb_last_cuda_error(void);
@@ -63,11 +64,6 @@ int snb_device_wait_failed(void);
  * The benchmark times it to get the FP32 CUDA-core peak used in its roofline fractions.
  * scratch: at least 4 bytes of device memory. */
 int snb_probe_fp32(float* scratch, int iters, double* flops, void* stream);
-
-/* Runs a register-only loop of the max-plus inner step in instruction form `variant` (0..6; no
- * counterpart in the reference); *pairs = output-pairs processed, each two reduction steps.
- * scratch: at least 2 * SMs * 256 + 64 floats of device memory, first 64 read as operands. */
-int snb_probe_step(int variant, float* scratch, int iters, double* pairs, void* stream);
 
 /* ---- l-infinity distance ---------------------------------------------------------------- */
 
@@ -243,10 +239,24 @@ int snb_mean_shift_apply(const float* x, const float* mean, const int* index, in
 /* out [lists, count] int32: for each list an independent, uniformly random subset of
  * {0 .. channels-1} with exactly `count` elements, ascending.  Deterministic in (seed, lists,
  * channels, count).  channels <= 51200.  Replaces sample_mask (core/models/norm_dist.py:14-17:
- * uniform scores + top-k in PyTorch; the reference leaves the lists unsorted, the order carries no
- * meaning); the caller draws `count` ~ Binomial(channels, keep rate) itself because it fixes the
+ * uniform scores + top-k + sort in PyTorch); the caller draws `count` ~ Binomial(channels, keep rate) itself because it fixes the
  * tensor shapes. */
 int snb_sample_mask(int* out, int lists, int channels, int count, unsigned long long seed, void* stream);
+
+/* Debug aid: checks caller-made index lists (index [lists, count] int32, i.e. the [S, G, count] lists
+ * of one operand) before they are handed to the kernels, which read w through them unchecked like
+ * the reference's (inf_dist_cuda.cu:163-172).  Returns SNB_STATUS_INDEX_RANGE when an entry lies
+ * outside [0, channels); *flags (host pointer, may be NULL) receives bit 0 = out of range, bit 1 =
+ * some list is not strictly ascending (legal, but the kernels gather fastest from ascending lists
+ * and the argmax tie rule "lowest compact index" then means "lowest channel").  Runs a small kernel
+ * and synchronises `stream`: not for the training loop.  sortnet_b200.norm_dist_cuda calls it for
+ * every index list when SORTNET_B200_DEBUG=1.  No counterpart in the reference. */
+int snb_check_index_lists(const int* index, int lists, int count, int channels, int* flags, void* stream);
+
+/* Hands the scratch that grouped / spatial calls (G > 1 or HW > 1) left in the library's memory pool of
+ * the current device back to the driver; the pool otherwise keeps up to 2 GiB of it for reuse.
+ * No counterpart in the reference. */
+int snb_trim_scratch(void);
 
 /* ---- optimiser ------------------------------------------------------------------------------- */
 
@@ -272,11 +282,27 @@ int snb_adamw_reduce_step(const float* w_src, float* w_dst, const void* const* g
  * the flat gradient buffers of all `world` ranks (peer pointers of one NVLink node, entry `rank`
  * its own), divides by world, applies AdamW with its shard-sized moments m, v and stores the new
  * parameter values into every rank's flat parameter buffer.  lo, hi multiples of 4; all pointers
- * 16-byte aligned; world <= 16.  The caller orders ranks with barriers before and after.
+ * 16-byte aligned; world <= 16.  The caller orders ranks with barriers (snb_peer_barrier) before and
+ * after.
  * Replaces DistributedDataParallel's all-reduce plus optimizer.step() (main.py:402,95). */
 int snb_dp_adamw_step(const void* const* grad_ptrs, void* const* param_ptrs, float* m, float* v, int rank,
                       int world, long long lo, long long hi, float lr, float beta1, float beta2, float eps,
                       float weight_decay, int step, void* stream);
+
+/* Stream-ordered barrier between the `world` (<= 16) ranks of one NVLink node, one process per GPU:
+ * enqueues one small kernel that stores `epoch` into every peer's flag word for this rank (release,
+ * system scope) and waits until this rank's own flag words hold `epoch` or later.  flag_ptrs: host
+ * array of `world` pointers to the ranks' flag arrays (`world` 32-bit words each, zero-initialised,
+ * mapped into this process; entry `rank` is this GPU's own).  Every barrier on the same flags
+ * passes the next epoch (1, 2, 3, ...), the same on all ranks.  The wait is bounded: after
+ * timeout_ns nanoseconds the kernel writes 1 + (rank it gave up on) into *status (any
+ * device-accessible int, e.g. pinned host memory, 0 on entry) and returns; nothing traps or hangs,
+ * and the host reads *status when it next synchronises.  What ran after a failed barrier read
+ * stale data and must be discarded.
+ * Replaces the ordering DistributedDataParallel gets from NCCL (main.py:402); the reference has
+ * no time-out (a missing rank hangs it). */
+int snb_peer_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch,
+                     unsigned long long timeout_ns, int* status, void* stream);
 
 #ifdef __cplusplus
 }

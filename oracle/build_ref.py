@@ -1,14 +1,19 @@
-"""Builds the reference's own CUDA extension for sm_100a into oracle/_ref/ (TEST INFRASTRUCTURE).
+"""Builds the reference's own CUDA extension for sm_100a into oracle/_ref/ and stages the
+reference's operator / layer / model Python beside it (TEST INFRASTRUCTURE).
 
     python -m oracle.build_ref            # needs the reference checkout, see REF below
 
-The sources are compiled where they lie (core/cuda/norm_dist.cpp and the four .cu files of
-zbh2047/SortNet); nothing is copied into this repository and the output directory is
-git-ignored.  The resulting module is imported by the GPU tests as a second checker (the real
-reference kernels on the same inputs) and by the benchmark as the GPU comparator.  It is never
-on the product path.
+The CUDA sources are compiled where they lie (core/cuda/norm_dist.cpp and the four .cu files of
+zbh2047/SortNet).  The Python files the drop-in claim is about (core/norm_dist.py,
+core/models/*.py, ell_inf_models.py) are placed, byte for byte, under oracle/_ref/py/ so that a
+machine without the checkout can still import the *unmodified* reference code.  The whole
+output directory is git-ignored: nothing of the reference enters this repository's history.
+
+Users: the GPU tests (the real reference kernels and the real reference model as second
+checkers), the benchmark's GPU comparator and its CPU arm.  Never the product path.
 """
 import os
+import shutil
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -16,14 +21,37 @@ OUT = os.path.join(HERE, "_ref")
 # checkout of zbh2047/SortNet: $SORTNET_REFERENCE, else a directory "reference" beside this repository
 REF = os.environ.get("SORTNET_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 SOURCES = ["norm_dist.cpp", "inf_dist_cuda.cu", "norm_dist_cuda.cu", "bound_inf_dist_cuda.cu", "sort_neuron.cu"]
+PY_OUT = os.path.join(OUT, "py")
+PY_FILES = ["ell_inf_models.py", "core/norm_dist.py", "core/models/__init__.py", "core/models/norm_dist.py",
+            "core/models/bound_basic_module.py"]
 
 
 def built_path():
     return os.path.join(OUT, "norm_dist_cuda.so")
 
 
+def staged_python():
+    """Directory holding the staged reference Python (to put on sys.path), or None."""
+    ok = all(os.path.exists(os.path.join(PY_OUT, f)) for f in PY_FILES)
+    return PY_OUT if ok else None
+
+
+def stage_python(force: bool = False):
+    """Copies the reference's Python files of this path into oracle/_ref/py/ unchanged."""
+    if staged_python() and not force:
+        return PY_OUT
+    if not all(os.path.exists(os.path.join(REF, f)) for f in PY_FILES):
+        return None
+    for f in PY_FILES:
+        dst = os.path.join(PY_OUT, f)
+        os.makedirs(os.path.dirname(dst), exist_ok=True)
+        shutil.copyfile(os.path.join(REF, f), dst)
+    return PY_OUT
+
+
 def build(force: bool = False):
     """Returns the path of the built module, or None when the reference checkout is absent."""
+    stage_python(force)
     if os.path.exists(built_path()) and not force:
         return built_path()
     src_dir = os.path.join(REF, "core", "cuda")
@@ -46,6 +74,25 @@ def build(force: bool = False):
         if f.endswith(".o") or f.endswith(".d") or f in ("build.ninja", "lock", ".ninja_log", ".ninja_deps"):
             os.remove(os.path.join(OUT, f))
     return built_path()
+
+
+def import_reference_python(extension_module):
+    """Imports the staged, unmodified reference Python with `extension_module` standing where its
+    `import norm_dist_cuda as _C` looks.  Returns (core.norm_dist, core.models, ell_inf_models) or
+    None when nothing is staged.  Later calls rebind the operator layer's `_C` to the module given,
+    which is how one process runs the same reference code over two different extensions."""
+    path = staged_python()
+    if path is None:
+        return None
+    import importlib
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    sys.modules["norm_dist_cuda"] = extension_module
+    ops = importlib.import_module("core.norm_dist")
+    ops._C = extension_module
+    models = importlib.import_module("core.models")
+    nets = importlib.import_module("ell_inf_models")
+    return ops, models, nets
 
 
 def load():

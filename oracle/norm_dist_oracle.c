@@ -222,22 +222,37 @@ void oracle_norm_dist_backward(const float *g, const float *x, const float *w, c
                                const int *ci, const int *co, int W_CO, int W_CI) {
     memset(gx, 0, sizeof(double) * (size_t)B * CI);
     if (gw) memset(gw, 0, sizeof(double) * (size_t)W_CO * W_CI);
-    for (int b = 0; b < B; b++) {
-        int s = b / SUB_BATCH;
-        const float *xb = x + (size_t)b * CI;
-        for (int j = 0; j < CO; j++) {
-            int row = co ? co[(size_t)s * CO + j] : j;
-            const float *wj = w + (size_t)row * W_CI;
-            double gv = g[(size_t)b * CO + j];
-            double ry = 1.0 / (double)y[(size_t)b * CO + j];
-            for (int c = 0; c < CI; c++) {
-                int col = w_col(ci, s, CI, c);
-                float t = xb[c] - wj[col];
-                double term = gv * pow(fabs((double)t) * ry, p - 1.0);
-                if (t < 0) term = -term;
-                gx[(size_t)b * CI + c] += term;
-                if (gw) gw[(size_t)row * W_CI + col] -= term;
+    /* Sub-batches one after the other; inside one, threads take different outputs j.  The kept
+     * rows of a sub-batch are distinct, so no two threads touch the same row of gw; grad_x is
+     * summed per thread and merged at the end of the sub-batch. */
+    int S = (B + SUB_BATCH - 1) / SUB_BATCH;
+    for (int s = 0; s < S; s++) {
+        int b0 = s * SUB_BATCH, b1 = b0 + SUB_BATCH < B ? b0 + SUB_BATCH : B;
+#pragma omp parallel
+        {
+            double *loc = (double *)calloc((size_t)(b1 - b0) * CI, sizeof(double));
+#pragma omp for schedule(static)
+            for (int j = 0; j < CO; j++) {
+                int row = co ? co[(size_t)s * CO + j] : j;
+                const float *wj = w + (size_t)row * W_CI;
+                for (int b = b0; b < b1; b++) {
+                    const float *xb = x + (size_t)b * CI;
+                    double gv = g[(size_t)b * CO + j];
+                    double ry = 1.0 / (double)y[(size_t)b * CO + j];
+                    double *lb = loc + (size_t)(b - b0) * CI;
+                    for (int c = 0; c < CI; c++) {
+                        int col = w_col(ci, s, CI, c);
+                        float t = xb[c] - wj[col];
+                        double term = gv * pow(fabs((double)t) * ry, p - 1.0);
+                        if (t < 0) term = -term;
+                        lb[c] += term;
+                        if (gw) gw[(size_t)row * W_CI + col] -= term;
+                    }
+                }
             }
+#pragma omp critical
+            for (size_t i = 0; i < (size_t)(b1 - b0) * CI; i++) gx[(size_t)b0 * CI + i] += loc[i];
+            free(loc);
         }
     }
 }

@@ -1,6 +1,6 @@
 """Runs one operator on one synthetic shape and prints its time (CUDA events).
 
-    python -m sortnet_b200.run_case --op bound_nograd --B 512 --CI 5120 --CO 5120 --iters 5
+    python run_case.py --op bound_nograd --B 512 --CI 5120 --CO 5120 --iters 5
 
 Used for quick timing of a single kernel and as the small, self-terminating command that
 profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_nograd,
@@ -8,25 +8,33 @@ inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_s
 sort_bound, sort_fwd (values + positions), sort_bwd (K = 10, q = 0.9), probe (hardware probes).
 """
 import argparse
+import ctypes
+import os
+import sys
 
 import torch
 
-from . import norm_dist_cuda as C
-from .layers import sample_mask
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from sortnet_b200 import _lib                      # noqa: E402
+from sortnet_b200 import norm_dist_cuda as C       # noqa: E402
+from sortnet_b200.layers import sample_mask        # noqa: E402
 
 OPS_PER_ELEMENT = {"inf_fwd": 2, "inf_nograd": 2, "bound_nograd": 6, "bound_fwd": 6, "lp_fwd": 4, "lp_bwd": 6, "lp_bwd_x": 6}
 
 
 PROBES = ["packed sub + max3abs", "2 scalar sub + 2 max", "2 scalar sub + max3abs", "packed sub + 2 max",
-          "max3abs alone", "interval-bound step (2 sub, min3, max3 per element)", "p=8 step (sub2, mul2, mul2, fma2)"]
+          "max3abs alone", "interval-bound step (2 sub, min3, max3 per element)", "p=8 step (sub2, mul2, mul2, fma2)",
+          "2 scalar sub + 2 sign clears + integer max3", "integer max3 alone"]
 
 
 def probe():
     """Times the FP32 FMA probe and every instruction form of the inner step; prints element
     rates per clock per SM using the SM clock NVML reports while the probes run."""
-    import ctypes
-    from . import _lib
     lib = _lib.load()
+    # declared in sortnet_b200/csrc/probe.h (bench-only, not part of the product header)
+    lib.snb_probe_step.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double),
+                                   ctypes.c_void_p]
+    lib.snb_probe_step.restype = ctypes.c_int
     dev = torch.device("cuda", 0)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     scratch = torch.linspace(0, 1, 2 * sms * 256 + 64, device=dev)

@@ -39,8 +39,9 @@ SIGNATURES = {
     "snb_adamw_step": [_P, _P, _P, _P, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _F, _P],
     "snb_adamw_reduce_step": [_P, _P, _P, _I, _P, _P, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _F, _P],
     "snb_dp_adamw_step": [_P, _P, _P, _P, _I, _I, ctypes.c_longlong, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _P],
+    "snb_peer_barrier": [_P, _I, _I, ctypes.c_uint, ctypes.c_ulonglong, _P, _P],
+    "snb_check_index_lists": [_P, _I, _I, _I, ctypes.POINTER(ctypes.c_int), _P],
     "snb_probe_fp32": [_P, _I, ctypes.POINTER(ctypes.c_double), _P],
-    "snb_probe_step": [_I, _P, _I, ctypes.POINTER(ctypes.c_double), _P],
 }
 
 
@@ -72,6 +73,8 @@ def load(build_if_missing: bool = False):
     lib.snb_last_cuda_error.restype = ctypes.c_char_p
     lib.snb_version.argtypes = []
     lib.snb_version.restype = ctypes.c_int
+    lib.snb_trim_scratch.argtypes = []
+    lib.snb_trim_scratch.restype = ctypes.c_int
     lib.snb_device_wait_failed.argtypes = []
     lib.snb_device_wait_failed.restype = ctypes.c_int
     lib.snb_inf_dist_forward_noalloc_max_outputs.argtypes = []

@@ -303,10 +303,11 @@ static cudaError_t launch_bound(BoundParams p, cudaStream_t st) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
     constexpr int SMEM = 2 * (2 * BM + BN) * LDS * (int)sizeof(float);
     auto kern = bound_fwd_kernel<WM, WN, VEC>;
-    static int ctas_per_sm[64] = {};
+    static std::atomic<int> ctas_per_sm[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    int& cps = ctas_per_sm[dev & 63];
+    std::atomic<int>& slot = ctas_per_sm[dev & 63];
+    int cps = slot.load(std::memory_order_acquire);
     if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
@@ -314,6 +315,7 @@ static cudaError_t launch_bound(BoundParams p, cudaStream_t st) {
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
         if (e != cudaSuccess) return e;
         cps = occ > 0 ? occ : 1;
+        slot.store(cps, std::memory_order_release);
     }
     p.tiles_m = (p.B + BM - 1) / BM;
     p.tiles_n = (p.CO + BN - 1) / BN;
@@ -337,12 +339,11 @@ using namespace snb;
 
 // SNB_DISABLE_TMA=1 in the environment keeps the cp.async staging everywhere.
 static bool tma_enabled() {
-    static int cached = -1;
-    if (cached < 0) {
+    static const bool enabled = [] {
         const char* e = getenv("SNB_DISABLE_TMA");
-        cached = (e && e[0] == '1') ? 0 : 1;
-    }
-    return cached == 1;
+        return !(e && e[0] == '1');
+    }();
+    return enabled;
 }
 
 static int check_bound(const void* xl, const void* xu, const void* w, const void* yl, const void* yu,
@@ -393,13 +394,13 @@ extern "C" int snb_bound_inf_dist_forward(const float* xl, const float* xu, cons
     const bool vec = (CI % 4 == 0) && aligned16(xl) && aligned16(xu) && aligned16(w);
     dim3 grid((B + 63) / 64, (CO + 63) / 64);
     constexpr int SMEM = 2 * 3 * 64 * LDS * (int)sizeof(float);
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
         SNB_CUDA(cudaFuncSetAttribute(bound_fwd_pos_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         SNB_CUDA(cudaFuncSetAttribute(bound_fwd_pos_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     if (vec) bound_fwd_pos_kernel<true><<<grid, 256, SMEM, (cudaStream_t)stream>>>(p);
     else bound_fwd_pos_kernel<false><<<grid, 256, SMEM, (cudaStream_t)stream>>>(p);

@@ -56,10 +56,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-#ifndef SNB_TMA_TN
-#define SNB_TMA_TN 8
-#endif
-constexpr int TMA_TN = SNB_TMA_TN;                                // output columns per thread (8 or 4)
+constexpr int TMA_TN = 8;                                         // output columns per thread
 constexpr int TMA_BM = 128, TMA_BN = 128, TMA_NT = 256 * 8 / TMA_TN, TMA_STAGES = 4;
 constexpr int TMA_TILE_FLOATS = 128 * BK;                         // 16 KiB
 constexpr int TMA_STAGE_FLOATS = 3 * TMA_TILE_FLOATS;             // x_L, x_U, W
@@ -218,15 +215,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 static EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static std::once_flag once;
+    std::call_once(once, [] {
         void* ptr = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
+    });
     return fn;
 }
 
@@ -249,13 +245,13 @@ cudaError_t bound_forward_tma(const float* xl, const float* xu, const float* w, 
     if (CI % 4 != 0 || !aligned16(xl) || !aligned16(xu) || !aligned16(w)) return cudaErrorNotSupported;
     CUtensorMap ml, mu, mw;
     if (!make_map(&ml, xl, B, CI) || !make_map(&mu, xu, B, CI) || !make_map(&mw, w, CO, CI)) return cudaErrorNotSupported;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(bound_fwd_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TMA_SMEM);
         if (e != cudaSuccess) return e;
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     BoundTmaParams p{yl, yu, B, CO, CI, (B + TMA_BM - 1) / TMA_BM, (CO + TMA_BN - 1) / TMA_BN};
     const long long tiles = (long long)p.tiles_m * p.tiles_n;

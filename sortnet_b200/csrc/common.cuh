@@ -18,6 +18,7 @@ enum {
     SNB_ERR_CUDA = 5,             // a CUDA runtime call failed (see snb_last_cuda_error)
     SNB_ERR_ALIGNMENT = 6,
     SNB_ERR_STATIC_CAPACITY = 7,  // B * CO exceeds the built-in scratch of the no-allocation entry point
+    SNB_ERR_INDEX_RANGE = 8,      // an index list holds an entry outside [0, channels) (snb_check_index_lists)
 };
 
 namespace snb {

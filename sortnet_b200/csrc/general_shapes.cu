@@ -72,6 +72,19 @@ __global__ void expand_mask_kernel(const int* __restrict__ m, int* __restrict__ 
 
 inline int grid_for(long long n) { return (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16); }
 
+// The library's own memory pools, one per device, created on first use (see Arena::commit).
+// Freed scratch up to SCRATCH_KEEP_BYTES stays in a pool between calls; snb_trim_scratch() hands
+// it back to the driver.
+constexpr unsigned long long SCRATCH_KEEP_BYTES = 2ull << 30;
+inline std::mutex& pool_mutex() {
+    static std::mutex m;
+    return m;
+}
+inline cudaMemPool_t* pool_table() {
+    static cudaMemPool_t pools[64] = {};
+    return pools;
+}
+
 // One stream-ordered allocation carved into 256-byte aligned pieces.
 class Arena {
   public:
@@ -86,14 +99,16 @@ class Arena {
     }
     cudaError_t commit() {
         // A memory pool of this library's own per device, with the release threshold raised so that
-        // freed scratch stays in the pool and the next call reuses it (a pool with the default
-        // threshold of 0 hands its memory back to the driver at the next synchronisation, which made
-        // every call pay for fresh physical memory).  The device's default pool is left alone.
-        static cudaMemPool_t pools[64] = {};
+        // freed scratch (up to 2 GiB) stays in the pool and the next call reuses it (a pool with the
+        // default threshold of 0 hands its memory back to the driver at the next synchronisation,
+        // which made every call pay for fresh physical memory).  The device's default pool is left
+        // alone.  The table is guarded: two host threads may make their first call at once.
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
         if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(pool_mutex());
+        cudaMemPool_t* pools = pool_table();
         if (!pools[dev]) {
             cudaMemPoolProps props = {};
             props.allocType = cudaMemAllocationTypePinned;
@@ -103,7 +118,7 @@ class Arena {
             cudaMemPool_t pool;
             e = cudaMemPoolCreate(&pool, &props);
             if (e != cudaSuccess) return e;
-            unsigned long long keep = ~0ull;
+            unsigned long long keep = SCRATCH_KEEP_BYTES;
             e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
             if (e != cudaSuccess) return e;
             pools[dev] = pool;
@@ -429,3 +444,16 @@ int general_sort_backward(const float* g_, const int* pos, int B, int CO, int CI
 }
 
 }  // namespace snb
+
+// Returns the scratch that the grouped / spatial shapes left in this library's memory pool of the
+// current device to the driver (the pool keeps up to 2 GiB of freed scratch for reuse otherwise).
+// Synchronises nothing; memory still in use by queued work stays until that work has finished.
+extern "C" int snb_trim_scratch(void) {
+    int dev = 0;
+    SNB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SNB_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(snb::pool_mutex());
+    cudaMemPool_t pool = snb::pool_table()[dev];
+    if (pool) SNB_CUDA(cudaMemPoolTrimTo(pool, 0));
+    return SNB_OK;
+}

@@ -17,10 +17,6 @@
 #include "launch.h"
 #include "general_shapes.h"
 
-#ifndef SNB_LINF_FORM
-#define SNB_LINF_FORM 0
-#endif
-
 namespace snb {
 
 struct InfFwdParams {
@@ -39,34 +35,15 @@ constexpr int CHUNK_TILES = 1;  // argmax chunk = one k-tile = 32 reduction step
 enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
 
 // Four reduction steps of one output: acc = max(acc, |x_k - w_k|), k = 0..3, operands given as
-// two 64-bit register pairs each.  All instruction forms of subtract + max cost two issue cycles
-// per element on sm_100a; the form is chosen for the fewest auxiliary instructions.
+// two 64-bit register pairs each: packed subtracts + three-input |.|-max.  All instruction forms of
+// subtract + max cost two issue cycles per element on sm_100a (scalar subtract + two-input max and
+// the mixed forms were measured); this one needs the fewest auxiliary instructions.
 __device__ __forceinline__ void linf_step(float& acc, const ulonglong2& x, const ulonglong2& w) {
-#if SNB_LINF_FORM == 1      // scalar subtracts + three-input max
-    float x0, x1, x2, x3, w0, w1, w2, w3;
-    unpack2(x.x, x0, x1);
-    unpack2(x.y, x2, x3);
-    unpack2(w.x, w0, w1);
-    unpack2(w.y, w2, w3);
-    acc = max3abs(acc, x0 - w0, x1 - w1);
-    acc = max3abs(acc, x2 - w2, x3 - w3);
-#elif SNB_LINF_FORM == 2    // scalar subtracts + two-input max
-    float x0, x1, x2, x3, w0, w1, w2, w3;
-    unpack2(x.x, x0, x1);
-    unpack2(x.y, x2, x3);
-    unpack2(w.x, w0, w1);
-    unpack2(w.y, w2, w3);
-    acc = fmaxf(acc, fabsf(x0 - w0));
-    acc = fmaxf(acc, fabsf(x1 - w1));
-    acc = fmaxf(acc, fabsf(x2 - w2));
-    acc = fmaxf(acc, fabsf(x3 - w3));
-#else                       // packed subtracts + three-input max
     float a, b;
     unpack2(sub2(x.x, w.x), a, b);
     acc = max3abs(acc, a, b);
     unpack2(sub2(x.y, w.y), a, b);
     acc = max3abs(acc, a, b);
-#endif
 }
 
 // Turns the chunk id left in pos by the tracking kernel into the reference's argmax word.
@@ -350,10 +327,11 @@ static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
     constexpr int SMEM = 2 * (BM + BN) * LDS * (int)sizeof(float);
     auto kern = inf_fwd_sk_kernel<WM, WN, MODE, TRACK>;
-    static int ctas_per_sm[64] = {};
+    static std::atomic<int> ctas_per_sm[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    int& cps = ctas_per_sm[dev & 63];
+    std::atomic<int>& slot = ctas_per_sm[dev & 63];
+    int cps = slot.load(std::memory_order_acquire);
     if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
@@ -361,6 +339,7 @@ static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
         if (e != cudaSuccess) return e;
         cps = occ > 0 ? occ : 1;
+        slot.store(cps, std::memory_order_release);
     }
     p.tiles_m = (p.B + BM - 1) / BM;
     p.tiles_n = (p.CO + BN - 1) / BN;
@@ -489,18 +468,20 @@ static __device__ __align__(256) unsigned long long snb_noalloc_keys[SNB_NOALLOC
 // only a handle for the runtime, not a pointer a kernel could use, so the address is looked up
 // once per device with that device current and cached.
 static cudaError_t noalloc_keys_address(unsigned long long** out) {
-    static unsigned long long* cached[64] = {};
+    static std::atomic<unsigned long long*> cached[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (!cached[dev]) {
+    unsigned long long* keys = cached[dev].load(std::memory_order_acquire);
+    if (!keys) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, snb_noalloc_keys);
         if (e != cudaSuccess) return e;
-        cached[dev] = static_cast<unsigned long long*>(ptr);
+        keys = static_cast<unsigned long long*>(ptr);
+        cached[dev].store(keys, std::memory_order_release);     // every thread looks up the same address
     }
-    *out = cached[dev];
+    *out = keys;
     return cudaSuccess;
 }
 

@@ -3,6 +3,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 namespace snb {
 
 // Records the last CUDA runtime error seen by an entry point of this thread.

@@ -481,10 +481,11 @@ template <int IP>
 static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
     constexpr int NT = 128;
     constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * LPB_GLD) * (int)sizeof(float);
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    int& cps = cached[dev & 63];
+    std::atomic<int>& slot = cached[dev & 63];
+    int cps = slot.load(std::memory_order_acquire);
     auto kern = lp_bwd_kernel<IP, NT>;
     if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -492,6 +493,7 @@ static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
         if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, SMEM);
         if (e != cudaSuccess) return e;
         cps = occ > 0 ? occ : 1;
+        slot.store(cps, std::memory_order_release);
     }
     const long long total = (long long)((q.B + 31) / 32) * ((q.CI + NT - 1) / NT) * ((q.CO + LPB_JT - 1) / LPB_JT);
     const long long slots = (long long)sm_count() * cps;
@@ -508,16 +510,18 @@ static cudaError_t launch_lp_fwd(LpFwdParams p, cudaStream_t st) {
     constexpr int BN = 64 * WN;
     constexpr int SMEM = 2 * (32 + BN) * LDS * (int)sizeof(float);
     auto kern = lp_fwd_kernel<WN, MODE, IP, NORM>;
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    int& cps = cached[dev & 63];
+    std::atomic<int>& slot = cached[dev & 63];
+    int cps = slot.load(std::memory_order_acquire);
     if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         int occ = 0;
         if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, WN * 32, SMEM);
         if (e != cudaSuccess) return e;
         cps = occ > 0 ? occ : 1;
+        slot.store(cps, std::memory_order_release);
     }
     const long long tiles = (long long)((p.B + 31) / 32) * ((p.CO + BN - 1) / BN);
     const long long slots = (long long)sm_count() * cps;

@@ -75,6 +75,13 @@ __global__ void __launch_bounds__(256) step_probe_kernel(const float* in, float*
                     const uint64_t t = sub2(xf[i], wf[j]);
                     const uint64_t t2 = mul2(t, t), t4 = mul2(t2, t2);
                     unpack2(fma2(t4, t4, pack2(acc[i][j], accl[i][j])), acc[i][j], accl[i][j]);
+                } else if (V == 7) {  // two scalar subtracts, sign bits cleared, integer three-input max
+                    // (non-negative floats order like their bit patterns)
+                    const int ia = __float_as_int(xa - wa) & 0x7fffffff, ib = __float_as_int(xb - wb) & 0x7fffffff;
+                    acc[i][j] = __int_as_float(__vimax3_s32(__float_as_int(acc[i][j]), ia, ib));
+                } else if (V == 8) {  // integer three-input max alone
+                    acc[i][j] = __int_as_float(__vimax3_s32(__float_as_int(acc[i][j]), __float_as_int(xa),
+                                                            __float_as_int(wb)));
                 }
             }
         }
@@ -103,7 +110,7 @@ extern "C" int snb_probe_fp32(float* scratch, int iters, double* flops, void* st
     return SNB_OK;
 }
 
-// Launches inner-step probe `variant` (0..6, see step_probe_kernel); *pairs receives the number
+// Launches inner-step probe `variant` (0..8, see step_probe_kernel); *pairs receives the number
 // of output-pairs processed (each pair = two reduction steps).  scratch: >= 2 * SMs * 256 + 64
 // floats, its first 64 floats are read as operands.
 extern "C" int snb_probe_step(int variant, float* scratch, int iters, double* pairs, void* stream) {
@@ -119,6 +126,8 @@ extern "C" int snb_probe_step(int variant, float* scratch, int iters, double* pa
         case 4: step_probe_kernel<4><<<blocks, 256, 0, st>>>(scratch, out, iters); break;
         case 5: step_probe_kernel<5><<<blocks, 256, 0, st>>>(scratch, out, iters); break;
         case 6: step_probe_kernel<6><<<blocks, 256, 0, st>>>(scratch, out, iters); break;
+        case 7: step_probe_kernel<7><<<blocks, 256, 0, st>>>(scratch, out, iters); break;
+        case 8: step_probe_kernel<8><<<blocks, 256, 0, st>>>(scratch, out, iters); break;
         default: return SNB_ERR_UNSUPPORTED;
     }
     SNB_CUDA(cudaGetLastError());

@@ -9,14 +9,13 @@ static thread_local cudaError_t g_last = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last = e; }
 
 int sm_count() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    int& c = cached[dev & 63];
+    int c = cached[dev & 63].load(std::memory_order_relaxed);
     if (c == 0) {
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-        c = v;
+        if (cudaDeviceGetAttribute(&c, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || c <= 0) c = 148;
+        cached[dev & 63].store(c, std::memory_order_relaxed);
     }
     return c;
 }
@@ -35,6 +34,7 @@ extern "C" const char* snb_status_string(int status) {
         case SNB_ERR_STATIC_CAPACITY:
             return "B * CO exceeds the built-in scratch of snb_inf_dist_forward_noalloc (1048576 outputs); "
                    "use snb_inf_dist_forward or snb_inf_dist_forward_ws";
+        case SNB_ERR_INDEX_RANGE: return "an index list holds an entry outside [0, channels)";
         default: return "unknown status";
     }
 }

@@ -134,9 +134,43 @@ __global__ void __launch_bounds__(SM_THREADS) sample_mask_kernel(int* __restrict
     }
 }
 
+// Validation of caller-made index lists (debug aid): bit 0 = an entry outside [0, channels),
+// bit 1 = a list that is not strictly ascending.
+__device__ int snb_index_check_bits;
+
+__global__ void check_index_kernel(const int* __restrict__ idx, long long n, int count, int channels) {
+    int bits = 0;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int v = idx[i];
+        if (v < 0 || v >= channels) bits |= 1;
+        if (i % count != 0 && idx[i - 1] >= v) bits |= 2;
+    }
+    if (bits) atomicOr(&snb_index_check_bits, bits);
+}
+
 }  // namespace snb
 
 using namespace snb;
+
+// index [lists, count] int32 (the [S, G, count] lists of one operand flattened): checks that every
+// entry lies in [0, channels) and whether every list is strictly ascending.  Copies the verdict
+// back and synchronises `stream`, so it is meant for debugging, not for the training loop.
+// *flags (host, optional) receives bit 0 = out of range, bit 1 = not ascending.
+extern "C" int snb_check_index_lists(const int* index, int lists, int count, int channels, int* flags, void* stream) {
+    if (!index) return SNB_ERR_NULL_POINTER;
+    if (lists <= 0 || count <= 0 || channels <= 0) return SNB_ERR_BAD_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    int bits = 0;
+    SNB_CUDA(cudaMemcpyToSymbolAsync(snb_index_check_bits, &bits, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+    const long long n = (long long)lists * count;
+    const int blocks = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    check_index_kernel<<<blocks, 256, 0, st>>>(index, n, count, channels);
+    SNB_CUDA(cudaGetLastError());
+    SNB_CUDA(cudaMemcpyFromSymbolAsync(&bits, snb_index_check_bits, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    SNB_CUDA(cudaStreamSynchronize(st));
+    if (flags) *flags = bits;
+    return (bits & 1) ? SNB_ERR_INDEX_RANGE : SNB_OK;
+}
 
 extern "C" int snb_sample_mask(int* out, int lists, int channels, int count, unsigned long long seed,
                                void* stream) {
@@ -144,12 +178,12 @@ extern "C" int snb_sample_mask(int* out, int lists, int channels, int count, uns
     if (lists <= 0 || channels <= 0 || count <= 0 || count > channels) return SNB_ERR_BAD_SHAPE;
     const size_t smem = sizeof(uint32_t) * (size_t)((channels + 3) / 4 * 4);
     if (smem > 200 * 1024) return SNB_ERR_TOO_LARGE;  // 51200 channels
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     SNB_CUDA(cudaGetDevice(&dev));
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
         SNB_CUDA(cudaFuncSetAttribute(sample_mask_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     sample_mask_kernel<<<lists, SM_THREADS, smem, (cudaStream_t)stream>>>(out, channels, count, (uint32_t)seed,
                                                                          (uint32_t)(seed >> 32));

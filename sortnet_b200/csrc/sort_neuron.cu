@@ -485,13 +485,13 @@ static cudaError_t launch_sort_fwd(const SortParams& p, cudaStream_t st) {
     constexpr int BM = 32, BN = (BOUND || KMAX <= 10) ? 32 : 64;
     constexpr int SMEM = 2 * ((BOUND ? 2 : 1) * BM + BN) * LDS * (int)sizeof(float);
     auto kern = sort_fwd_kernel<KMAX, BOUND>;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     dim3 grid((p.B + BM - 1) / BM, (p.CO + BN - 1) / BN);
     kern<<<grid, 256, SMEM, st>>>(p);

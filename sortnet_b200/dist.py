@@ -15,6 +15,11 @@ import torch.distributed as dist
 class GradientAllReduce:
     def __init__(self, params, process_group=None):
         self.params = [p for p in params if p.requires_grad]
+        if any(getattr(p, "grad_sink", None) is not None for p in self.params):
+            # optim.FlatAdamW has taken these parameters over: their gradients are written into its flat
+            # buffer and never reach .grad, so the hooks below would never fire
+            raise ValueError("parameters managed by FlatAdamW exchange their gradients through it "
+                             "(FlatAdamW.all_reduce or its peer-memory step), not through GradientAllReduce")
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self._pending = []

@@ -377,20 +377,31 @@ class SortMLPModel(nn.Module):
         return masks
 
     @torch.no_grad()
-    def certified_margin(self, x, targets, eps, up, down):
-        """Evaluation-mode l-inf interval-bound pass over the box [x - eps, x + eps] clipped to
-        [down, up]: every layer propagates the point value and the bounds with the plain
-        l-inf distance (keep rate 1), running means are subtracted.  Returns the fraction of
-        rows whose worst-case margin is negative for every wrong class (certified accuracy)."""
+    def certified_margin(self, x, targets, eps, up, down, sort_eval=None):
+        """Evaluation-mode interval-bound pass over the box [x - eps, x + eps] clipped to
+        [down, up], running means subtracted.  Returns the fraction of rows whose worst-case
+        margin is negative for every wrong class.
+
+        sort_eval=None (default) propagates what `forward()` propagates in evaluation mode: the
+        sort neuron and its bounds for layers with a keep rate below 1, the plain l-inf distance
+        and `bound_inf_dist` otherwise -- the returned fraction is then the certified accuracy of
+        the network that is actually evaluated (main.py:205-240 does the same through the model's
+        forward).  sort_eval=False forces the plain l-inf distance and its interval bounds in
+        every layer, whatever the keep rates: that is the l-inf interval-bound workload
+        (bound_inf_dist_cuda.cu), and a certificate only for a network whose keep rates are all 1;
+        for a sort-neuron network the number it returns is NOT a certified accuracy, because the
+        sort neuron's output lies below the l-inf distance."""
         was_training = self.training
         self.eval()
+        if sort_eval is None:
+            sort_eval = any(l.keep_rate != 1.0 for l in self.fc_dist)
         try:
             x = x.reshape(x.size(0), -1)
             lower = torch.maximum(x - eps, down)
             upper = torch.minimum(x + eps, up)
             for layer in self.fc_dist:
                 assert math.isinf(layer.p)
-                x, lower, upper = layer(x, lower, upper, sort_eval=False)
+                x, lower, upper = layer(x, lower, upper, sort_eval=sort_eval and layer.keep_rate != 1.0)
             score_lo, score_hi = -upper, -lower
             margin = score_hi - torch.gather(score_lo, 1, targets.view(-1, 1))
             margin = margin.scatter(1, targets.view(-1, 1), float("-inf"))

@@ -4,12 +4,17 @@
 Every function writes into caller-allocated tensors and returns None, like the reference.
 Differences: work is enqueued on PyTorch's *current* stream of the tensors' device (the
 reference always uses the legacy default stream, forward.cuh:31), the device of the inputs is
-made current for the call, and shapes / dtypes / index ranges that the reference leaves
-unchecked raise RuntimeError instead of corrupting memory.
+made current for the call, and shapes / dtypes that the reference leaves unchecked raise
+RuntimeError instead of corrupting memory.  The *values* of index lists are not looked at on the
+normal path (the kernels read w through them unchecked, like the reference's); with
+SORTNET_B200_DEBUG=1 in the environment every index list is validated on the device before use
+(`snb_check_index_lists`: one small kernel and a stream synchronisation per list) and an entry
+outside [0, channels) raises.
 
 `install()` registers this module as `norm_dist_cuda` in sys.modules so that the reference's
 unmodified `core/norm_dist.py` (`import norm_dist_cuda as _C`) runs on these kernels.
 """
+import os
 import sys
 
 import torch
@@ -17,6 +22,7 @@ import torch
 from . import _lib
 
 _SUB_BATCH = 32
+DEBUG_INDEX_CHECKS = os.environ.get("SORTNET_B200_DEBUG", "0") == "1"
 
 
 def _check(t, name, dtype=torch.float32):
@@ -28,14 +34,34 @@ def _check(t, name, dtype=torch.float32):
         raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
 
 
-def _check_opt_index(t, name, n_sub, width, groups=1):
-    """Index lists are [sub-batches, groups, kept channels per group]; `width` is the total over groups."""
+def _check_opt_index(t, name, n_sub, width, groups=1, channels=None):
+    """Index lists are [sub-batches, groups, kept channels per group]; `width` is the total over
+    groups; `channels` (when the caller knows it) is the size of the axis of w the entries index,
+    per group, used by the optional value check."""
     if t is None:
         return
     _check(t, name, torch.int32)
     if t.dim() != 3 or t.size(0) != n_sub or t.size(1) != groups or t.size(2) * groups != width:
         raise RuntimeError("%s must have shape [%d, %d, %d], got %s"
                            % (name, n_sub, groups, width // max(groups, 1), tuple(t.shape)))
+    if DEBUG_INDEX_CHECKS and channels is not None:
+        check_index_lists(t, channels, name)
+
+
+def check_index_lists(index, channels, name="index"):
+    """Validates the values of an index tensor [S, G, count] on its device: raises when an entry lies
+    outside [0, channels); returns True when every list is strictly ascending.  Synchronises."""
+    import ctypes
+    _check(index, name, torch.int32)
+    flags = ctypes.c_int(0)
+    with torch.cuda.device(index.device):
+        rc = _lib.load().snb_check_index_lists(index.data_ptr(), index.size(0) * index.size(1), index.size(2),
+                                               int(channels), ctypes.byref(flags),
+                                               torch.cuda.current_stream(index.device).cuda_stream)
+    if rc == 8:
+        raise RuntimeError("%s holds an entry outside [0, %d)" % (name, channels))
+    _lib.check(rc, "check_index_lists")
+    return not (flags.value & 2)
 
 
 def _ptr(t):
@@ -117,8 +143,8 @@ def inf_dist_forward(input, weight, output, pos, G, w_index_ci=None, w_index_co=
     _check(pos, "pos", torch.int32)
     B, CO, CI, HW = _dims(input, output)
     S = (B + _SUB_BATCH - 1) // _SUB_BATCH
-    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G)
-    _check_opt_index(w_index_co, "w_index_co", S, CO, G)
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G, weight.size(1))
+    _check_opt_index(w_index_co, "w_index_co", S, CO, G, weight.size(0) // G)
     if output.size(0) != B or pos.shape != output.shape:
         raise RuntimeError("output / pos shape mismatch")
     dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
@@ -159,8 +185,8 @@ def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
     _check(grad_input, "grad_input"); _check(grad_weight, "grad_weight")
     B, CO, CI, HW = grad_output.size(0), grad_output.size(1), grad_input.size(1), grad_output.size(2)
     S = (B + _SUB_BATCH - 1) // _SUB_BATCH
-    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G)
-    _check_opt_index(w_index_co, "w_index_co", S, CO, G)
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G, grad_weight.size(1))
+    _check_opt_index(w_index_co, "w_index_co", S, CO, G, grad_weight.size(0) // G)
     if pos.shape != grad_output.shape or grad_input.size(0) != B:
         raise RuntimeError("shape mismatch between grad_output, pos and grad_input")
     dev = _same_device(grad_output, pos, grad_input, grad_weight, w_index_ci, w_index_co)
@@ -172,8 +198,8 @@ def inf_dist_backward_input_weight(grad_output, pos, grad_input, grad_weight, G,
 def _lp_common(input, weight, output, w_index_ci, w_index_co, G):
     B, CO, CI, HW = _dims(input, output)
     S = (B + _SUB_BATCH - 1) // _SUB_BATCH
-    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G)
-    _check_opt_index(w_index_co, "w_index_co", S, CO, G)
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, G, weight.size(1))
+    _check_opt_index(w_index_co, "w_index_co", S, CO, G, weight.size(0) // G)
     return B, CO, CI, HW
 
 
@@ -195,6 +221,8 @@ def norm_dist_forward_with_max(input, weight, max_output, output, G, p, w_index_
     """core/cuda/norm_dist.cpp:67-85.  Never called by the reference's Python code; provided for
     completeness.  The supplied maximum is not needed: the result equals norm_dist_forward's."""
     _check(max_output, "max_output")
+    if max_output.shape != output.shape:
+        raise RuntimeError("max_output must have the shape of output")
     norm_dist_forward(input, weight, output, G, p, w_index_ci, w_index_co)
 
 

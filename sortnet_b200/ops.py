@@ -58,9 +58,13 @@ def _dist_backward(ctx, grad_y):
     ci, co = ctx.masks
     grad_x = torch.empty_like(x)
     # A weight that carries `grad_sink` (a tensor of its shape, see optim.FlatAdamW) gets its
-    # gradient written there and autograd receives None for it: nothing is copied or accumulated.
+    # gradient written there and autograd receives None for it: nothing is copied or accumulated
+    # in the usual case of one backward per step.  The kernels overwrite their grad_weight, so a
+    # sink that this step has already written (a second backward before the optimiser step, a
+    # weight used twice in one graph) is added to through a temporary instead.
     sink = getattr(weight, "grad_sink", None) if need_w else None
-    grad_w = (sink if sink is not None else torch.empty_like(weight)) if need_w else None
+    add_to_sink = sink is not None and getattr(weight, "grad_sink_written", False)
+    grad_w = (sink if (sink is not None and not add_to_sink) else torch.empty_like(weight)) if need_w else None
     if math.isinf(ctx.p):
         if need_w:
             _C.inf_dist_backward_input_weight(grad_y, third, grad_x, grad_w, ctx.group, ci, co)
@@ -71,6 +75,10 @@ def _dist_backward(ctx, grad_y):
             _C.norm_dist_backward_input_weight(grad_y, x, weight, third, grad_x, grad_w, ctx.group, ctx.p, ci, co)
         elif need_x:
             _C.norm_dist_backward_input(grad_y, x, weight, third, grad_x, ctx.group, ctx.p, ci, co)
+    if sink is not None:
+        if add_to_sink:
+            sink.add_(grad_w)
+        weight.grad_sink_written = True
     return (grad_x if need_x else None), (None if sink is not None else grad_w)
 
 

@@ -9,11 +9,18 @@ The reference uses torch.optim.AdamW on ordinary parameters behind DistributedDa
 (main.py:402,429-432); parameter names, shapes and values are unchanged here (each parameter
 becomes a view into the flat buffer), so state_dicts stay interchangeable.
 """
+import ctypes
+import os
+
 import torch
 import torch.distributed as dist
 
 from . import _lib
 from . import norm_dist_cuda as _C
+
+# Only plain peer loads, stores and copies are used here: keep symmetric memory off the NVLink
+# multicast objects (a rank that dies while bound to one disturbs its peers' GPUs).
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 def _pad4(n):
@@ -42,7 +49,7 @@ class FlatAdamW:
     """
 
     def __init__(self, module, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0, process_group=None,
-                 peer_memory=False, overlap=False):
+                 peer_memory=False, overlap=False, barrier_timeout_s=10.0):
         """peer_memory=True (ranks of one NVLink node): the flat gradient and parameter buffers are
         allocated as symmetric memory and `step()` runs the fused reduce-scatter + AdamW +
         all-gather kernel over peer pointers instead of an NCCL all-reduce plus a local update;
@@ -53,7 +60,12 @@ class FlatAdamW:
         every peer's gradients (copy engines over NVLink, no SM time), the local sum + AdamW kernel
         and copies of the updated shard into every peer's *second* parameter buffer;
         `end_exchange()` makes the main stream wait for them and switches the parameters to that
-        buffer.  Kernels launched in between (the interval-bound pass) keep reading the old values."""
+        buffer.  Kernels launched in between (the interval-bound pass) keep reading the old values.
+
+        Ranks are ordered by `snb_peer_barrier` kernels on the exchange's stream.  Their wait is
+        bounded by `barrier_timeout_s`: a rank that does not arrive makes its peers' barrier give up
+        and record which rank was missing; `check()` (called by `end_exchange()` / `step()` and by
+        whoever reads results back) turns that record into an exception.  Nothing traps or hangs."""
         self.params = [p for p in module.parameters() if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")
@@ -69,7 +81,6 @@ class FlatAdamW:
         self.numel = total
         self.peer = bool(peer_memory) and self.world > 1
         if self.peer:
-            import ctypes
             import torch.distributed._symmetric_memory as symm_mem
             group = process_group if process_group is not None else dist.group.WORLD
             self.flat_param = symm_mem.empty(total, dtype=torch.float32, device=dev)
@@ -86,6 +97,21 @@ class FlatAdamW:
             self.lo, self.hi = shard_bounds(total, self.world, self.rank)
             moments = max(self.hi - self.lo, 4)
             self.overlap = bool(overlap)
+            # barrier state: one 32-bit flag per peer in symmetric memory, an epoch counter that all
+            # ranks advance in step, and a status word in pinned host memory that the barrier kernel
+            # writes when it gives up (read by check() without synchronising)
+            self._flags = symm_mem.empty(max(self.world, 4), dtype=torch.int32, device=dev)
+            self._flags.zero_()
+            self._hdl_flags = symm_mem.rendezvous(self._flags, group)
+            self._flag_ptrs = arr(*[int(q) for q in self._hdl_flags.buffer_ptrs])
+            self._epoch = 0
+            self._timeout_ns = int(barrier_timeout_s * 1e9)
+            self._status = torch.zeros(1, dtype=torch.int32).pin_memory()
+            torch.cuda.synchronize(dev)
+            dist.barrier(group)                       # every rank's flags are zero before anyone signals
+            for ptr in list(self._grad_ptrs) + list(self._param_ptrs):
+                if not ptr or ptr % 16:
+                    raise ValueError("peer buffers must be non-null and 16-byte aligned")
             if self.overlap:
                 self._setup_overlap(symm_mem, group, total, dev)
         else:
@@ -97,12 +123,15 @@ class FlatAdamW:
         self.exp_avg_sq = torch.zeros(moments, device=dev, dtype=torch.float32)
         self._slices = []
         self._views = [[], []]          # parameter views into the two parameter buffers (overlap)
+        self._failed = None
+        self._grads_prepared = False
         for p, off in zip(self.params, offsets):
             view = self.flat_param[off:off + p.numel()].view_as(p)
             view.copy_(p.data)
             p.data = view
             sink = self.flat_grad[off:off + p.numel()].view_as(p)
             p.grad_sink = sink
+            p.grad_sink_written = False
             self._slices.append((p, sink))
             if self.overlap:
                 self._views[0].append(view)
@@ -128,12 +157,37 @@ class FlatAdamW:
         self._done = torch.cuda.Event()
         self._in_flight = False
 
+    def _barrier(self, stream):
+        """Enqueues the bounded inter-rank barrier on `stream`; raises at once if it cannot be launched."""
+        self._epoch += 1
+        rc = _lib.load().snb_peer_barrier(self._flag_ptrs, self.rank, self.world, self._epoch, self._timeout_ns,
+                                          self._status.data_ptr(), stream.cuda_stream)
+        if rc != 0:
+            self._failed = "peer barrier could not be launched"
+        _lib.check(rc, "peer_barrier")
+        _C.launch_count += 1
+
+    def check(self):
+        """Raises if a barrier of an earlier step gave up on a peer (reads a pinned host word, no
+        synchronisation) or if this rank failed to enqueue part of an exchange.  The parameters of a
+        step whose barrier failed were built from incomplete data and must be discarded."""
+        if self._failed:
+            raise RuntimeError("data-parallel step failed on this rank: %s" % self._failed)
+        if self.peer and int(self._status[0]) != 0:
+            raise RuntimeError("rank %d did not reach the gradient-exchange barrier within %.1f s"
+                               % (int(self._status[0]) - 1, self._timeout_ns * 1e-9))
+
     def begin_exchange(self):
         """Queues the gradient exchange and the update of this rank's shard behind everything that
-        is on the current stream now (the backward); returns at once."""
+        is on the current stream now (the backward); returns at once.
+
+        Every launch status is examined before the next operation is queued: a rank that cannot
+        launch stops there (pushing nothing, signalling nothing) and raises, and its peers' next
+        barrier runs into its time limit and reports this rank through check()."""
         if not self.overlap:
             raise RuntimeError("begin_exchange() needs FlatAdamW(peer_memory=True, overlap=True)")
-        import ctypes
+        self.check()
+        self._prepare_grads()
         self.step_count += 1
         dev = self.flat_grad.device
         lo, hi, n = self.lo, self.hi, self.hi - self.lo
@@ -143,8 +197,7 @@ class FlatAdamW:
             self._side.wait_event(self._ready)
             with torch.cuda.stream(self._side):
                 # every rank's backward has finished writing its gradients ...
-                self._hdl_grad.barrier(channel=0, timeout_ms=60000)
-                rc = 0
+                self._barrier(self._side)
                 if n > 0:
                     for r, src in self._peer_grad.items():
                         self._recv[r].copy_(src, non_blocking=True)
@@ -155,13 +208,16 @@ class FlatAdamW:
                         self.exp_avg_sq.data_ptr(), n, float(self.lr), float(self.betas[0]), float(self.betas[1]),
                         float(self.eps), float(self.weight_decay), self.step_count, 1.0 / self.world,
                         self._side.cuda_stream)
+                    if rc != 0:
+                        self._failed = "the shard update could not be launched"
+                    _lib.check(rc, "adamw_reduce_step")
+                    _C.launch_count += 1
                     for r, dst in self._peer_param[self._cur ^ 1].items():
                         dst.copy_(nxt[lo:hi], non_blocking=True)
                 # ... and every rank's shard of the new values has landed in this rank's second buffer
-                self._param_hdls[self._cur ^ 1].barrier(channel=0, timeout_ms=60000)
+                self._barrier(self._side)
                 self._done.record(self._side)
-        _lib.check(rc, "adamw_reduce_step")
-        _C.launch_count += 1
+        self._grads_consumed()
         self._in_flight = True
 
     def end_exchange(self):
@@ -170,6 +226,7 @@ class FlatAdamW:
             raise RuntimeError("end_exchange() without begin_exchange()")
         dev = self.flat_grad.device
         torch.cuda.current_stream(dev).wait_event(self._done)
+        self.check()
         self._cur ^= 1
         self.flat_param = self._param_bufs[self._cur]
         for p, view in zip(self.params, self._views[self._cur]):
@@ -177,22 +234,46 @@ class FlatAdamW:
         self._in_flight = False
 
     def zero_grad(self):
-        """Only autograd-owned gradients need clearing; sinks are overwritten by the backward."""
+        """Autograd-owned gradients are dropped; the sinks are marked unwritten (the first backward
+        of the step overwrites them, further ones add, see ops._dist_backward)."""
         for p in self.params:
             p.grad = None
+            p.grad_sink_written = False
+        self._grads_prepared = False
 
     def gather_grads(self):
-        """Copies gradients that autograd produced itself (parameters whose operator does not
-        write into the sink) into the flat buffer."""
+        """Moves gradients that autograd produced itself (parameters whose operator does not
+        write into the sink) into the flat buffer, adding to what the step already wrote there."""
         for p, sink in self._slices:
             if p.grad is not None:
-                sink.copy_(p.grad)
+                if p.grad_sink_written:
+                    sink.add_(p.grad)
+                else:
+                    sink.copy_(p.grad)
+                    p.grad_sink_written = True
                 p.grad = None
+
+    def _prepare_grads(self):
+        """Before the gradients are consumed: a parameter that no backward reached since the last
+        step (or zero_grad()) has a zero gradient, not the previous step's.  Idempotent within a step."""
+        if self._grads_prepared:
+            return
+        for p, sink in self._slices:
+            if not p.grad_sink_written:
+                sink.zero_()
+        self._grads_prepared = True
+
+    def _grads_consumed(self):
+        """After the update has been queued: the next backward overwrites the sinks again."""
+        for p in self.params:
+            p.grad_sink_written = False
+        self._grads_prepared = False
 
     def all_reduce(self, async_op=False):
         """Sums the flat gradient over ranks (one collective); the mean is taken inside step()."""
         if self.world == 1 or self.peer:
             return None            # with peer memory the exchange is part of step()
+        self._prepare_grads()
         return dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
 
     def step(self):
@@ -200,21 +281,27 @@ class FlatAdamW:
             self.begin_exchange()
             self.end_exchange()
             return
+        self.check()
+        self._prepare_grads()
         self.step_count += 1
         dev = self.flat_param.device
         if self.peer:
             with torch.cuda.device(dev):
-                st = torch.cuda.current_stream(dev).cuda_stream
+                stream = torch.cuda.current_stream(dev)
                 # every rank's backward has finished writing its gradients ...
-                self._hdl_grad.barrier(channel=0, timeout_ms=60000)
+                self._barrier(stream)
                 rc = _lib.load().snb_dp_adamw_step(
                     self._grad_ptrs, self._param_ptrs, self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
                     self.rank, self.world, self.lo, self.hi, float(self.lr), float(self.betas[0]),
-                    float(self.betas[1]), float(self.eps), float(self.weight_decay), self.step_count, st)
+                    float(self.betas[1]), float(self.eps), float(self.weight_decay), self.step_count,
+                    stream.cuda_stream)
+                if rc != 0:
+                    self._failed = "the fused exchange kernel could not be launched"
+                _lib.check(rc, "dp_adamw_step")
+                _C.launch_count += 1
                 # ... and every rank's new parameters have landed here before the next forward
-                self._hdl_param.barrier(channel=0, timeout_ms=60000)
-            _lib.check(rc, "dp_adamw_step")
-            _C.launch_count += 1
+                self._barrier(stream)
+            self._grads_consumed()
             return
         with torch.cuda.device(dev):
             rc = _lib.load().snb_adamw_step(
@@ -224,3 +311,4 @@ class FlatAdamW:
                 1.0 / self.world, torch.cuda.current_stream(dev).cuda_stream)
         _lib.check(rc, "adamw_step")
         _C.launch_count += 1
+        self._grads_consumed()

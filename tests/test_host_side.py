@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol(built_lib):
 def test_loader_signatures_cover_the_header(built_lib):
     from sortnet_b200 import _lib
     utility = {"snb_status_string", "snb_last_cuda_error", "snb_version", "snb_inf_dist_forward_workspace_bytes",
-               "snb_inf_dist_forward_noalloc_max_outputs", "snb_device_wait_failed",
+               "snb_inf_dist_forward_noalloc_max_outputs", "snb_device_wait_failed", "snb_trim_scratch",
                "snb_norm_dist_forward_workspace_bytes"}
     assert set(_lib.SIGNATURES) | utility == set(declared_symbols())
     lib = _lib.load()

@@ -99,3 +99,30 @@ def test_update_running_means_is_the_average_of_batch_means():
     want = torch.stack(means).mean(dim=0)
     got = model.fc_dist[0].mean_shift.running_mean
     assert (got - want).abs().max() <= 1e-5 * want.abs().max()
+
+
+@pytest.mark.parametrize("keep", [0.8, 1.0])
+def test_certified_margin_agrees_with_the_evaluation_forward(keep):
+    """The certified fraction must be the one the evaluation-mode forward certifies (the sort neuron
+    and its bounds when the keep rate is below 1); sort_eval=False is the plain l-inf bound
+    workload and differs for such a model."""
+    from sortnet_b200.layers import SortMLPModel
+    torch.manual_seed(5)
+    model = SortMLPModel(depth=4, width=128, input_dim=(3, 4, 4), num_classes=10, dropout=keep, std=0.3).cuda()
+    for l in model.fc_dist:
+        if l.mean_shift is not None:
+            l.mean_shift.running_mean.normal_(1.0, 0.2)
+    x = torch.rand(96, 3, 4, 4, device="cuda")
+    with torch.no_grad():
+        t = model.eval()(x).argmax(dim=1)          # labels the network gets right: margins near the boundary
+    eps = 0.002
+    up, down = torch.ones(1, device="cuda"), torch.zeros(1, device="cuda")
+    with torch.no_grad():
+        _, margin = model(x, targets=t, eps=eps, up=up, down=down)
+    want = (margin.scatter(1, t.view(-1, 1), float("-inf")).max(dim=1)[0] < 0).float().mean()
+    got = model.certified_margin(x, t, eps, up, down)
+    assert float(got) == float(want)
+    assert not model.training
+    plain = model.certified_margin(x, t, eps, up, down, sort_eval=False)
+    if keep == 1.0:
+        assert float(plain) == float(got)

@@ -1,8 +1,11 @@
 """GPU parity of the finite-p kernels against the exact-math (float64) oracle.
 
-Tolerance: 1e-5 relative (max-abs error over max-abs value per tensor) for outputs and
-gradients at p <= 32.  For larger p the fp32 rounding of |t| / y alone is amplified by p - 1
-(6e-8 * (p - 1)), so the gradient tolerance is widened to 3e-7 * p there."""
+Tolerance: outputs are gated element by element, |y - y_o| <= 1e-5 * |y_o| (all distances are
+positive and of order one, so every element can be held to the bar).  Gradients are sums of
+signed terms accumulated with atomics in run-dependent order, so they are gated tensor-wise:
+max-abs error over max-abs value <= 1e-5 at p <= 32.  For larger p the fp32 rounding of |t| / y
+alone is amplified by p - 1 (6e-8 * (p - 1)), so the gradient tolerance is widened to 3e-7 * p
+there."""
 import numpy as np
 import pytest
 import torch
@@ -13,6 +16,13 @@ from gpu_util import col3, dev, host, idx3, make_masks, rel
 pytestmark = pytest.mark.gpu
 
 TOL = 1e-5
+
+
+def rel_each(y, y_o):
+    """Largest element-wise relative error of positive outputs."""
+    y = np.asarray(y, np.float64)
+    y_o = np.asarray(y_o, np.float64)
+    return float((np.abs(y - y_o) / np.abs(y_o)).max())
 
 
 def run_fwd(x, w, p, ci=None, co=None):
@@ -41,7 +51,7 @@ def test_golden(golden, name):
     p = float(g["p"])
     ci, co = g.get("ci"), g.get("co")
     y = run_fwd(g["x"], g["w"], p, ci, co)
-    assert rel(y, g["y"]) < TOL
+    assert rel_each(y, g["y"]) < 2e-5                  # the fixture itself is fp32 torch
     gx, gw = run_bwd(g["gy"], g["x"], g["w"], y, p, ci, co)
     assert rel(gx, g["gx"]) < 2e-5 and rel(gw, g["gw"]) < 2e-5   # the fixture itself is fp32 torch
 
@@ -54,7 +64,7 @@ def test_unmasked_vs_oracle(p, B, CI, CO):
     w = rng.standard_normal((CO, CI)).astype(np.float32)
     y_o = oracle.norm_dist_forward(x, w, p)
     y = run_fwd(x, w, p)
-    assert rel(y, y_o) < TOL
+    assert rel_each(y, y_o) < TOL
     g = rng.standard_normal((B, CO)).astype(np.float32)
     gx_o, gw_o = oracle.norm_dist_backward(g, x, w, y, p)
     gx, gw = run_bwd(g, x, w, y, p)
@@ -75,7 +85,7 @@ def test_masked_vs_oracle(p, which):
     w = rng.standard_normal((CO, CI)).astype(np.float32)
     y_o = oracle.norm_dist_forward(x, w, p, ci, co)
     y = run_fwd(x, w, p, ci, co)
-    assert rel(y, y_o) < TOL
+    assert rel_each(y, y_o) < TOL
     g = rng.standard_normal(y.shape).astype(np.float32)
     gx_o, gw_o = oracle.norm_dist_backward(g, x, w, y, p, ci, co)
     gx, gw = run_bwd(g, x, w, y, p, ci, co)
@@ -89,7 +99,7 @@ def test_degenerate_rows():
     for p in (2.0, 8.0, 20.0):
         y = run_fwd(x, w, p)
         y_o = oracle.norm_dist_forward(x, w, p)
-        assert rel(y, y_o) < TOL
+        assert rel_each(y, y_o) < TOL
 
 
 def test_large_p_approaches_inf():
@@ -135,7 +145,7 @@ def test_entry_point_without_scratch(p, B, CI, CO, keep):
                                       ptr(CI_), ptr(CO_), CO, CI, ws.data_ptr(), n_ws, stream)
     assert rc == 0
     torch.cuda.synchronize()
-    assert rel(host(y_plain), y_o) < TOL and rel(host(y_ws), y_o) < TOL
+    assert rel_each(host(y_plain), y_o) < TOL and rel_each(host(y_ws), y_o) < TOL
     assert rel(host(y_plain), host(y_ws)) < 2e-6
     # a misaligned scratch pointer is refused, a short one falls back to the scratch-free kernel
     if p > 10:
@@ -146,3 +156,30 @@ def test_entry_point_without_scratch(p, B, CI, CO, keep):
                                             ptr(CI_), ptr(CO_), CO, CI, ws.data_ptr(), n_ws - 4, stream) == 0
         torch.cuda.synchronize()
         assert torch.equal(y_short, y_plain)
+
+
+@pytest.mark.parametrize("p", [3.0, 8.0, 31.6])
+@pytest.mark.parametrize("masked", [False, True], ids=["dense 64x5120x5120", "masked 64x4619x4596"])
+def test_wide_layers_vs_oracle(p, masked):
+    """Two sub-batches of a 5120-wide layer: more than 10 000 backward work units, so every thread
+    block's range spans several units and both the plain-store and the atomic branch of the
+    backward run; the forward runs shared tiles with atomically merged partial sums followed by
+    the root kernel.  Every element of y and both gradients against the exact-math oracle."""
+    B, CI, CO = 64, 5120, 5120
+    rng = np.random.default_rng(int(p * 10) + masked)
+    ci = co = None
+    if masked:
+        S = B // 32
+        ci = np.stack([np.sort(rng.permutation(CI)[:4619]) for _ in range(S)]).astype(np.int32)
+        co = np.stack([np.sort(rng.permutation(CO)[:4596]) for _ in range(S)]).astype(np.int32)
+    x = rng.random((B, ci.shape[1] if masked else CI), dtype=np.float32)
+    w = rng.standard_normal((CO, CI)).astype(np.float32)
+    y_o = oracle.norm_dist_forward(x, w, p, ci, co)
+    y = run_fwd(x, w, p, ci, co)
+    assert rel_each(y, y_o) < TOL
+    g = rng.standard_normal(y.shape).astype(np.float32)
+    gx_o, gw_o = oracle.norm_dist_backward(g, x, w, y, p, ci, co)
+    gx, gw = run_bwd(g, x, w, y, p, ci, co)
+    assert rel(gx, gx_o) < TOL and rel(gw, gw_o) < TOL
+    gx2, _ = run_bwd(g, x, w, y, p, ci, co, weight=False)
+    assert rel(gx2, gx_o) < TOL

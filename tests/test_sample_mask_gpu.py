@@ -88,3 +88,38 @@ def test_bad_arguments():
         C.sample_mask_into(out, 5, 1)              # more elements than channels
     with pytest.raises(RuntimeError):
         C.sample_mask_into(out.float(), 50, 1)     # wrong dtype
+
+
+def test_check_index_lists_flags_bad_entries_and_order():
+    """The debug validation of caller-made index lists (snb_check_index_lists)."""
+    from sortnet_b200 import norm_dist_cuda as C
+    good = torch.tensor([[[0, 3, 7, 9]], [[1, 2, 3, 4]]], dtype=torch.int32, device="cuda")
+    assert C.check_index_lists(good, 10) is True
+    unsorted = torch.tensor([[[0, 7, 3, 9]], [[1, 2, 3, 4]]], dtype=torch.int32, device="cuda")
+    assert C.check_index_lists(unsorted, 10) is False
+    repeated = torch.tensor([[[0, 3, 3, 9]]], dtype=torch.int32, device="cuda")
+    assert C.check_index_lists(repeated, 10) is False
+    for bad in ([[[0, 3, 7, 10]]], [[[-1, 3, 7, 9]]]):
+        with pytest.raises(RuntimeError, match="outside"):
+            C.check_index_lists(torch.tensor(bad, dtype=torch.int32, device="cuda"), 10)
+    # the last entry of one list may exceed the first of the next
+    two = torch.tensor([[[5, 9]], [[0, 1]]], dtype=torch.int32, device="cuda")
+    assert C.check_index_lists(two, 10) is True
+
+
+def test_debug_mode_validates_index_lists_before_the_kernels(monkeypatch):
+    from sortnet_b200 import norm_dist_cuda as C
+    monkeypatch.setattr(C, "DEBUG_INDEX_CHECKS", True)
+    x = torch.rand(32, 3, 1, device="cuda")
+    w = torch.randn(6, 5, device="cuda")
+    y = torch.empty(32, 2, 1, device="cuda")
+    pos = torch.empty(32, 2, 1, device="cuda", dtype=torch.int32)
+    ci = torch.tensor([[[0, 2, 4]]], dtype=torch.int32, device="cuda")
+    co = torch.tensor([[[1, 5]]], dtype=torch.int32, device="cuda")
+    C.inf_dist_forward(x, w, y, pos, 1, ci, co)
+    bad_ci = torch.tensor([[[0, 2, 5]]], dtype=torch.int32, device="cuda")      # w has 5 columns
+    with pytest.raises(RuntimeError, match="w_index_ci"):
+        C.inf_dist_forward(x, w, y, pos, 1, bad_ci, co)
+    bad_co = torch.tensor([[[1, 6]]], dtype=torch.int32, device="cuda")         # w has 6 rows
+    with pytest.raises(RuntimeError, match="w_index_co"):
+        C.inf_dist_forward(x, w, y, pos, 1, ci, bad_co)

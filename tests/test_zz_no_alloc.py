@@ -5,7 +5,8 @@ tensor library to lend it scratch; cudaMalloc synchronises the device and can fa
 budget).  For such callers the library carries its own fixed scratch array.  This file checks that
 the entry point returns exactly what the ordinary entry point returns (y and argmax words are
 compared bit for bit, the bar all l-infinity tests use), on two calls in a row with different
-inputs, since the array keeps whatever the previous call left in it.  It is named so that pytest
+inputs, since the array keeps whatever the previous call left in it; the first shape is also
+compared with the CPU oracle directly.  It is named so that pytest
 collects it last: if it fails, a run that stops at the first failure has already run every other
 test.  It does not depend on any other test having run.
 """
@@ -47,10 +48,15 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row():
     # is split as well, so stale keys of the first call lie inside and beyond the region it uses;
     # third call: a shape small enough to run without merging
     shapes = [(128, 784, 5120), (64, 2048, 2048), (96, 300, 1000)]
-    for B, CI, CO in shapes:
+    for k, (B, CI, CO) in enumerate(shapes):
         x = (torch.randint(0, 8, (B, CI, 1), device="cuda", generator=gen) / 8).float().contiguous()
         w = (torch.randint(-16, 17, (CO, CI), device="cuda", generator=gen) / 8).float().contiguous()
         (y0, p0), (y1, p1) = _forward_pair(lib, x, w)
+        if k == 0:
+            import oracle
+            y_o, pos_o = oracle.inf_dist_forward(x[:, :, 0].cpu().numpy(), w.cpu().numpy())
+            assert np.array_equal(y1[:, :, 0].cpu().numpy(), y_o), "values differ from the oracle"
+            assert np.array_equal(p1[:, :, 0].cpu().numpy(), pos_o), "argmax words differ from the oracle"
         assert torch.equal(y0, y1), "values differ from the ordinary entry point"
         assert torch.equal(p0, p1), "argmax words differ from the ordinary entry point"
         assert not torch.isnan(y1).any() and int(p1.min()) != -7
