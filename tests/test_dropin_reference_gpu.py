@@ -4,8 +4,10 @@ twice in one process -- once over this library (`sortnet_b200.norm_dist_cuda` st
 reference does `import norm_dist_cuda as _C`), once over the reference's own CUDA extension
 compiled for sm_100a -- on the same weights, inputs and seeded masks.
 
-Bars: l-inf values (logits, margins, running means) bit-exact; gradients 1e-5 (both sides sum
-them with atomics in their own order); finite p and the sort-neuron evaluation path 1e-5.
+Bars: l-inf values (logits, margins, running means) bit-exact; l-inf gradients 1e-5 (both sides
+sum them with atomics in their own order); finite-p values and the sort-neuron evaluation path
+1e-5; finite-p gradients 2e-5 for integer p and 1e-4 for general p (two fp32 implementations, each
+with its own error against exact arithmetic, see the test).
 Skipped when oracle/_ref holds no build (no reference checkout on the build machine)."""
 import copy
 
@@ -80,9 +82,11 @@ def test_reference_training_step_over_both_extensions(ref, keep, p):
     else:
         assert rel(a[0].cpu().numpy(), b[0].cpu().numpy()) < 1e-5
         assert rel(a[1].cpu().numpy(), b[1].cpu().numpy()) < 1e-5
-    # the reference's generic-p kernels use the approximate __powf: their own error against exact
-    # arithmetic is of the order of 1e-5 there, so the two sides are compared a little wider
-    tol = 1e-5 if (p == INF or p == float(int(p))) else 1e-4
+    # Two fp32 implementations are compared here, not one against exact arithmetic: at finite p each
+    # side is within 1e-5 of the exact-math oracle (tests/test_norm_dist_lp_gpu.py holds this library to
+    # that), so they may differ by twice that; the reference's generic-p kernels use the approximate
+    # __powf and are themselves a few 1e-5 off there.
+    tol = 1e-5 if p == INF else (2e-5 if p == float(int(p)) else 1e-4)
     for k in a[2]:
         assert rel(a[2][k].cpu().numpy(), b[2][k].cpu().numpy()) < tol, k
 
