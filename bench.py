@@ -338,8 +338,7 @@ def dp_check(job, dev, world):
                                     opt.step_count + 1, 1.0 / world, torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "adamw_step")
     # the selected exchange on the very same local gradients (mark them as this step's)
-    for prm in opt.params:
-        prm.grad_sink_written = True
+    opt.set_flat_grad()
     if job.exchange == "nccl":
         opt.all_reduce()
     opt.step()
@@ -470,9 +469,8 @@ def hbm_block(job):
     except Exception:
         pass
     def one_step():
-        for prm in opt.params:                 # keep the gradients of the last backward: the step then
-            prm.grad_sink_written = True       # is the update kernel alone, as inside a training step
-        opt.step()
+        opt.set_flat_grad()                    # keep the gradients of the last backward: the step then
+        opt.step()                             # is the update kernel alone, as inside a training step
 
     a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     one_step()

@@ -253,6 +253,15 @@ class FlatAdamW:
                     p.grad_sink_written = True
                 p.grad = None
 
+    def set_flat_grad(self, flat=None):
+        """Declares the flat gradient buffer to hold this step's gradients of all parameters (after
+        copying `flat` into it when given): for callers that fill the buffer themselves instead of
+        running a backward, e.g. to replay recorded gradients."""
+        if flat is not None:
+            self.flat_grad.copy_(flat)
+        for p in self.params:
+            p.grad_sink_written = True
+
     def _prepare_grads(self):
         """Before the gradients are consumed: a parameter that no backward reached since the last
         step (or zero_grad()) has a zero gradient, not the previous step's.  Idempotent within a step."""

@@ -55,7 +55,7 @@ def _worker(rank, world, port, out, overlap=False):
             opt_a.gather_grads()
             # both optimisers get the very same local gradients (Adam amplifies the run-to-run
             # rounding differences of atomically accumulated gradients where they cancel to ~0)
-            opt_b.flat_grad.copy_(opt_a.flat_grad)
+            opt_b.set_flat_grad(opt_a.flat_grad)
             opt_b.all_reduce()
             opt_b.step()
             if overlap:
