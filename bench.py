@@ -227,8 +227,7 @@ class Job:
         self.host_t = [torch.randint(0, cfg["classes"], (self.B,), generator=gen).pin_memory() for _ in range(pool)]
         self.dev_x = [t.to(dev) for t in self.host_x]
         self.dev_t = [t.to(dev) for t in self.host_t]
-        self.up = torch.ones(1, device=dev)
-        self.down = torch.zeros(1, device=dev)
+        self.up, self.down = 1.0, 0.0           # the box is clipped to the pixel range [0, 1]
         self.pool = pool
 
     def bound_pass(self, x, t):
@@ -242,8 +241,7 @@ class Job:
     def step(self, x, t, update=True, bounds=True):
         model, opt = self.model, self.opt
         model.train()
-        logits, margin = model(x, targets=t, eps=self.cfg["eps"])
-        loss = mixture_loss(logits, margin, t)
+        loss = model.mixture_loss(x, t, self.cfg["eps"])      # forward + margin + the reference's mixture loss
         opt.zero_grad()
         loss.backward()
         opt.gather_grads()
@@ -564,6 +562,7 @@ def gpu_comparator_block(job, steps=10, warmup=3):
     opt = torch.optim.AdamW(model.parameters(), **ADAM)
     eps = cfg["eps"]
     drop_list = ref_models.NormDistBase.dropout_list
+    up, down = torch.ones(1, device=dev), torch.zeros(1, device=dev)
 
     def bound_pass(x, t, faithful):
         model.eval()
@@ -572,7 +571,7 @@ def gpu_comparator_block(job, steps=10, warmup=3):
             drop_list.clear()                 # the reference's own branch for layers without a keep rate
         try:
             with torch.no_grad():
-                _, margin = model(x, targets=t, eps=eps, up=job.up, down=job.down)
+                _, margin = model(x, targets=t, eps=eps, up=up, down=down)
         finally:
             drop_list.clear()
             drop_list.update(saved)

@@ -258,6 +258,61 @@ int snb_check_index_lists(const int* index, int lists, int count, int channels, 
  * No counterpart in the reference. */
 int snb_trim_scratch(void);
 
+/* ---- whole layers and the model head (G = 1, HW = 1) ---------------------------------------- */
+
+/* One fully connected norm-distance layer of the training / plain forward in one call: the distance
+ * (p = inf: snb_inf_dist_forward_ws when pos is given, snb_inf_dist_forward_nograd when pos is NULL
+ * and there are no index lists; finite p: snb_norm_dist_forward_ws) into y_dist, then, when `mean`
+ * is not NULL, the batch mean per channel into mean [W_CO] with the momentum update of running_mean
+ * (may be NULL), and out[b, j] = (y_dist[b, j] - mean[c]) + bias[c] with c = w_index_co[s_b][j] (mean
+ * and bias optional; out may be y_dist).  workspace as in the _ws entry points (may be NULL).
+ * Replaces the chain norm_dist_dropout / norm_dist -> MeanShiftDropout.forward -> bias add of
+ * NormDistBase.forward (core/models/norm_dist.py:85-103; core/models/bound_basic_module.py:123-157). */
+int snb_layer_forward(const float* x, const float* w, int B, int CO, int CI, float p, const int* w_index_ci,
+                      const int* w_index_co, int W_CO, int W_CI, float* y_dist, int* pos, void* workspace,
+                      size_t workspace_bytes, float* running_mean, float momentum, float* mean, const float* bias,
+                      float* out, void* stream);
+
+/* Backward of snb_layer_forward: grad_bias [W_CO] (optional) = column sums of grad_out over the rows
+ * that kept each channel; with mean_shift != 0 the gradient is centred like the activations were
+ * (mean [W_CO] and grad_centred [B, CO] are scratch); then the distance backward into grad_x
+ * [B, CI] (NULL: stop after the bias gradient) and grad_w [W_CO, W_CI] (optional, zero-filled here).
+ * pos is needed for p = inf, x / w / y_dist for finite p.
+ * Replaces the autograd chain of the same Python code (core/norm_dist.py:75-99 for the operator). */
+int snb_layer_backward(const float* grad_out, const float* x, const float* w, const float* y_dist, const int* pos,
+                       int B, int CO, int CI, float p, const int* w_index_ci, const int* w_index_co, int W_CO,
+                       int W_CI, int mean_shift, float* mean, float* grad_centred, float* grad_bias, float* grad_x,
+                       float* grad_w, void* stream);
+
+/* One layer of the evaluation-mode l-inf interval-bound pass: y = l-inf distance of the point value x
+ * (x may be NULL), (yl, yu) = interval bounds of the box (xl, xu) (may be NULL), then running_mean
+ * subtracted from and bias added to all three (each optional).
+ * Replaces NormDistBase.forward in evaluation mode without a keep rate
+ * (core/models/norm_dist.py:93-103) and MeanShiftDropout's evaluation branch. */
+int snb_layer_bound_forward(const float* x, const float* xl, const float* xu, const float* w, int B, int CO, int CI,
+                            const float* running_mean, const float* bias, float* y, float* yl, float* yu,
+                            void* stream);
+
+/* xl = max(x - eps, down), xu = min(x + eps, up) over n values: the input box of the certification
+ * forward for scalar bounds.  Replaces ell_inf_models.py:35-36. */
+int snb_input_box(const float* x, float eps, float down, float up, long long n, float* xl, float* xu, void* stream);
+
+/* Head of the training step on the last layer's outputs d [B, K] with int64 targets:
+ * margin[b, c] = ((d[b, t] + eps) - (d[b, c] - eps)) / (2 eps), 0 at c = t (written when margin is
+ * not NULL); loss = mean_b (max_c clamp(margin, 0, clip) + lam * cross_entropy(-scale * d[b, :], t));
+ * grad_d [B, K] (optional) = d loss / d d.  row_loss [B] is scratch; *loss is a device float.
+ * Replaces ell_inf_models.py:45-50 and the `mixture` loss of main.py:357-364 with their autograd
+ * backward. */
+int snb_margin_loss(const float* d, const long long* target, int B, int K, float eps, float clip, float lam,
+                    float scale, float* margin, float* row_loss, float* loss, float* grad_d, void* stream);
+
+/* *fraction (device float) = share of rows b with max_{c != t} (yu[b, t] - yl[b, c]) < 0, i.e. whose
+ * worst-case margin from the bounds (yl, yu) [B, K] of the last layer is negative for every wrong
+ * class; row_flag [B] is scratch.  Replaces ell_inf_models.py:45-50 on the bounds plus the
+ * certified-accuracy count of main.py:225-227. */
+int snb_certified_fraction(const float* yl, const float* yu, const long long* target, int B, int K, float* row_flag,
+                           float* fraction, void* stream);
+
 /* ---- optimiser ------------------------------------------------------------------------------- */
 
 /* One AdamW step over flat buffers of n fp32 values (n a multiple of 4, 16-byte aligned), with the

@@ -85,6 +85,9 @@ def main():
     ap.add_argument("--p", type=float, default=8.0)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--rotate", type=int, default=1,
+                    help="number of weight matrices to rotate through (> 1: the weights of a call are not in L2, "
+                         "as inside a network whose layers have different weights)")
     a = ap.parse_args()
     if a.op == "probe":
         return probe()
@@ -97,7 +100,8 @@ def main():
         co = sample_mask(S, 1, a.CO, a.keep, dev)
     ci_n = a.CI if ci is None else ci.size(-1)
     co_n = a.CO if co is None else co.size(-1)
-    w = torch.randn(a.CO, a.CI, device=dev)
+    ws = [torch.randn(a.CO, a.CI, device=dev) for _ in range(max(a.rotate, 1))]
+    w = ws[0]
     x = torch.rand(a.B, ci_n, 1, device=dev)
     y = torch.empty(a.B, co_n, 1, device=dev)
     pos = torch.zeros(a.B, co_n, 1, device=dev, dtype=torch.int32)
@@ -117,7 +121,11 @@ def main():
         posk = torch.zeros(SORT_K, a.B, co_n, 1, device=dev, dtype=torch.int32)
         C.sort_neuron_forward(x, w, y, posk, 1, SORT_Q, SORT_K)
 
+    calls = [0]
+
     def run():
+        w = ws[calls[0] % len(ws)]
+        calls[0] += 1
         if a.op == "inf_fwd":
             C.inf_dist_forward(x, w, y, pos, 1, ci, co)
         elif a.op == "inf_nograd":

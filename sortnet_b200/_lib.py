@@ -39,6 +39,12 @@ SIGNATURES = {
     "snb_adamw_step": [_P, _P, _P, _P, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _F, _P],
     "snb_adamw_reduce_step": [_P, _P, _P, _I, _P, _P, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _F, _P],
     "snb_dp_adamw_step": [_P, _P, _P, _P, _I, _I, ctypes.c_longlong, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _P],
+    "snb_layer_forward": [_P, _P, _I, _I, _I, _F, _P, _P, _I, _I, _P, _P, _P, ctypes.c_size_t, _P, _F, _P, _P, _P, _P],
+    "snb_layer_backward": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P],
+    "snb_layer_bound_forward": [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P],
+    "snb_input_box": [_P, _F, _F, _F, ctypes.c_longlong, _P, _P, _P],
+    "snb_margin_loss": [_P, _P, _I, _I, _F, _F, _F, _F, _P, _P, _P, _P, _P],
+    "snb_certified_fraction": [_P, _P, _P, _I, _I, _P, _P, _P],
     "snb_peer_barrier": [_P, _I, _I, ctypes.c_uint, ctypes.c_ulonglong, _P, _P],
     "snb_check_index_lists": [_P, _I, _I, _I, ctypes.POINTER(ctypes.c_int), _P],
     "snb_probe_fp32": [_P, _I, ctypes.POINTER(ctypes.c_double), _P],

@@ -322,7 +322,10 @@ static cudaError_t launch_bound(BoundParams p, cudaStream_t st) {
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const long long units = tiles * ((p.CI + BK - 1) / BK);
     long long grid = (long long)sm_count() * cps;
-    if (tiles % grid == 0 || units < grid) grid = tiles;  // whole tiles already balance
+    // whole tiles when they balance anyway; a problem with fewer (tile, k-tile) pairs than resident
+    // CTAs (few tiles, e.g. a narrow head layer) still spreads over one CTA per pair
+    if (tiles % grid == 0) grid = tiles;
+    else if (units < grid) grid = units;
     p.split = (grid != tiles);
     if (p.split) {
         cudaError_t e = cudaMemsetAsync(p.yl, 0, sizeof(float) * (size_t)p.B * p.CO, st);

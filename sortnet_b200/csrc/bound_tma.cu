@@ -257,7 +257,8 @@ cudaError_t bound_forward_tma(const float* xl, const float* xu, const float* w, 
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const long long units = tiles * ((CI + BK - 1) / BK);
     long long grid = sm_count();   // one CTA per SM (192 KiB of tiles each)
-    if (tiles % grid == 0 || units < grid) grid = tiles;
+    if (tiles % grid == 0) grid = tiles;
+    else if (units < grid) grid = units;
     if (grid != tiles) {
         cudaError_t e = cudaMemsetAsync(yl, 0, sizeof(float) * (size_t)B * CO, st);
         if (e == cudaSuccess) e = cudaMemsetAsync(yu, 0, sizeof(float) * (size_t)B * CO, st);

@@ -346,7 +346,11 @@ static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const long long units = tiles * ((p.CI + BK - 1) / BK);
     long long grid = (long long)sm_count() * cps;
-    if (tiles % grid == 0 || units < grid || (TRACK && !p.keys)) grid = tiles;  // whole tiles
+    // whole tiles when they balance anyway or when there is nowhere to merge (value, chunk) pairs; a
+    // problem with fewer (tile, k-tile) pairs than resident CTAs (few tiles, e.g. a narrow head
+    // layer) still spreads over one CTA per pair
+    if (tiles % grid == 0 || (TRACK && !p.keys)) grid = tiles;
+    else if (units < grid) grid = units;
     *split = (grid != tiles);
     if (!*split) {
         p.keys = nullptr;

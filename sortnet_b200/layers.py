@@ -27,6 +27,9 @@ from . import norm_dist_cuda as _C
 from . import ops
 
 SUB_BATCH = 32
+# One library call per fully connected layer and direction where that applies (see NormDist.forward);
+# False takes the operators one by one everywhere (the results are the same).
+FUSED_LAYERS = True
 
 
 def sample_mask(batch, groups, channel, q, device, count=None):
@@ -234,8 +237,25 @@ class NormDist(nn.Module):
         Without masks: the l-p / l-inf distance of the point value and, when a box
         (lower, upper) is given, its interval bounds (p must be inf).  `sort_eval=True` replaces
         the distance by the deterministic sort neuron with q = `dropout` (the expectation of
-        the masked training-time neuron), as the reference does outside training."""
+        the masked training-time neuron), as the reference does outside training.
+
+        Two cases run as one library call per layer (distance + mean shift + bias together, see
+        ops.NormDistLayerF and snb_layer_bound_forward): the training-mode forward of the point
+        value, and the evaluation-mode l-inf pass without gradients.  Everything else takes the
+        operators one by one."""
         masked = mask_in is not None or mask_out is not None
+        box = lower is not None and upper is not None
+        if FUSED_LAYERS and x is not None and x.is_cuda and not sort_eval:
+            if self.training and not box:
+                rm = self.mean_shift.running_mean if self.mean_shift is not None else None
+                mom = self.mean_shift.momentum if self.mean_shift is not None else 0.0
+                y = ops.norm_dist_layer(x, self.weight, self.bias, self.p, _as_index32(mask_in),
+                                        _as_index32(mask_out), rm, mom)
+                return y, None, None
+            if (not self.training and not masked and math.isinf(self.p)
+                    and not (torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad
+                                                          or (box and (lower.requires_grad or upper.requires_grad))))):
+                return self._eval_linf(x, lower if box else None, upper if box else None)
         x3, l3, u3 = (None if z is None else z.unsqueeze(-1).contiguous() for z in (x, lower, upper))
         if masked:
             x3 = ops.norm_dist_dropout(x3, self.weight, mask_in, mask_out, self.p)
@@ -255,6 +275,20 @@ class NormDist(nn.Module):
             b = MeanShiftDropout._gathered(self.bias, mask_out, x3.size(0) if x3 is not None else l3.size(0))
             x3, l3, u3 = (None if z is None else z + b.unsqueeze(-1) for z in (x3, l3, u3))
         return tuple(None if z is None else z.squeeze(-1) for z in (x3, l3, u3))
+
+    def _eval_linf(self, x, lower, upper):
+        """Evaluation-mode l-inf layer without gradients: point value, interval bounds, running
+        mean and bias in one library call."""
+        x = x.contiguous()
+        B, dev = x.size(0), x.device
+        y = torch.empty(B, self.out_features, device=dev, dtype=torch.float32)
+        yl = yu = None
+        if lower is not None:
+            lower, upper = lower.contiguous(), upper.contiguous()
+            yl, yu = torch.empty_like(y), torch.empty_like(y)
+        rm = self.mean_shift.running_mean if self.mean_shift is not None else None
+        _C.layer_bound_forward(x, lower, upper, self.weight, rm, self.bias, y, yl, yu)
+        return y, yl, yu
 
     def extra_repr(self):
         return "in_features={}, out_features={}, bias={}, keep={}".format(
@@ -397,11 +431,22 @@ class SortMLPModel(nn.Module):
             sort_eval = any(l.keep_rate != 1.0 for l in self.fc_dist)
         try:
             x = x.reshape(x.size(0), -1)
-            lower = torch.maximum(x - eps, down)
-            upper = torch.minimum(x + eps, up)
+            scalars = isinstance(up, (int, float)) and isinstance(down, (int, float))
+            if FUSED_LAYERS and scalars and x.is_cuda:
+                x = x.contiguous()
+                lower, upper = torch.empty_like(x), torch.empty_like(x)
+                _C.input_box(x, eps, down, up, lower, upper)
+            else:
+                lower = torch.maximum(x - eps, torch.as_tensor(down, device=x.device))
+                upper = torch.minimum(x + eps, torch.as_tensor(up, device=x.device))
             for layer in self.fc_dist:
                 assert math.isinf(layer.p)
                 x, lower, upper = layer(x, lower, upper, sort_eval=sort_eval and layer.keep_rate != 1.0)
+            if FUSED_LAYERS and x.is_cuda:
+                frac = torch.empty((), device=x.device, dtype=torch.float32)
+                rows = torch.empty(x.size(0), device=x.device, dtype=torch.float32)
+                _C.certified_fraction(lower.contiguous(), upper.contiguous(), targets.contiguous(), rows, frac)
+                return frac
             score_lo, score_hi = -upper, -lower
             margin = score_hi - torch.gather(score_lo, 1, targets.view(-1, 1))
             margin = margin.scatter(1, targets.view(-1, 1), float("-inf"))
@@ -409,24 +454,35 @@ class SortMLPModel(nn.Module):
         finally:
             self.train(was_training)
 
-    def forward(self, x=None, targets=None, eps=0, up=None, down=None, masks=None):
-        x = x.reshape(x.size(0), -1)
-        lower = upper = None
-        if up is not None and down is not None and self._certifying():
-            lower = torch.maximum(x - eps, down.reshape(1, -1) if down.dim() else down)
-            upper = torch.minimum(x + eps, up.reshape(1, -1) if up.dim() else up)
+    def mixture_loss(self, x, targets, eps, lam=0.1, clip=1.0, masks=None):
+        """Training forward followed by the reference's `mixture` loss (main.py:357-364) on the
+        margin of ell_inf_models.py:45-50: mean_b max_c clamp(margin, 0, clip) + lam * cross_entropy.
+        Same value and gradients as `forward(x, targets, eps)` followed by that loss in PyTorch
+        ops; the head (margin, loss and its gradient) runs as one kernel."""
+        d = self._distances(x, masks)
+        if FUSED_LAYERS and d.is_cuda and not isinstance(self.scalar, torch.Tensor):
+            return ops.margin_loss(d, targets, eps, clip, lam, float(self.scalar))
+        score, margin = self._scores(d, None, None, targets, eps)
+        return margin.clamp(min=0, max=clip).max(dim=1)[0].mean() + lam * F.cross_entropy(score, targets)
+
+    def _distances(self, x, masks=None, lower=None, upper=None):
+        """Runs the layer stack; returns the head's outputs (and bounds when a box is given)."""
         has_dropout = any(l.keep_rate != 1.0 for l in self.fc_dist)
         use_masks = has_dropout and self.training and torch.is_grad_enabled()
         if use_masks and masks is None:
             masks = self.draw_masks(x.size(0), x.device)
+        x = x.reshape(x.size(0), -1)
         mask_in = None
         for k, layer in enumerate(self.fc_dist):
             mask_out = masks[k] if (use_masks and k < len(masks)) else None
             x, lower, upper = layer(x, lower, upper, mask_in=mask_in, mask_out=mask_out,
                                     sort_eval=has_dropout and not use_masks)
             mask_in = mask_out
-        if targets is None:
-            return -x * self.scalar
+        if lower is None:
+            return x
+        return x, lower, upper
+
+    def _scores(self, x, lower, upper, targets, eps):
         lo = x - eps if lower is None else lower
         hi = x + eps if upper is None else upper
         # distances -> scores: negate, so the roles of the bounds swap
@@ -434,6 +490,22 @@ class SortMLPModel(nn.Module):
         margin = score_hi - torch.gather(score_lo, 1, targets.view(-1, 1))
         margin = margin.scatter(1, targets.view(-1, 1), 0)
         return score * self.scalar, margin / (2 * eps)
+
+    def forward(self, x=None, targets=None, eps=0, up=None, down=None, masks=None):
+        x = x.reshape(x.size(0), -1)
+        lower = upper = None
+        if up is not None and down is not None and self._certifying():
+            up, down = (torch.as_tensor(z, device=x.device, dtype=x.dtype) for z in (up, down))
+            lower = torch.maximum(x - eps, down.reshape(1, -1) if down.dim() else down)
+            upper = torch.minimum(x + eps, up.reshape(1, -1) if up.dim() else up)
+        out = self._distances(x, masks, lower, upper)
+        if lower is not None:
+            x, lower, upper = out
+        else:
+            x = out
+        if targets is None:
+            return -x * self.scalar
+        return self._scores(x, lower, upper, targets, eps)
 
 
 @torch.no_grad()

@@ -417,6 +417,91 @@ def sample_mask_into(out, channels, seed):
           _ptr(out), lists, int(channels), count, int(seed) & 0xFFFFFFFFFFFFFFFF)
 
 
+# ---- whole layers and the model head (one C call each; G = 1, HW = 1, 2-D tensors) ---------------
+
+_LAYER_KERNELS = {"snb_layer_forward": 4, "snb_layer_backward": 4, "snb_layer_bound_forward": 3, "snb_input_box": 1,
+                  "snb_margin_loss": 2, "snb_certified_fraction": 2}
+
+
+def _layer_call(entry, tag, ref, *args):
+    """Lean variant of _call for the layer-level entry points: the callers in ops.py / layers.py own
+    every tensor they pass (fresh allocations of the right shape and dtype), so only the device is
+    looked after here."""
+    global launch_count
+    if _timeline is not None:
+        return _call(ref.device, ref, entry, tag, *args)
+    dev = ref.device
+    fn = getattr(_lib.load(), entry)
+    if torch.cuda.current_device() == dev.index:
+        rc = fn(*args, torch.cuda.current_stream(dev).cuda_stream)
+    else:
+        with torch.cuda.device(dev):
+            rc = fn(*args, torch.cuda.current_stream(dev).cuda_stream)
+    if rc:
+        _lib.check(rc, entry[4:])
+    launch_count += _LAYER_KERNELS[entry]
+
+
+_KERNELS.update(_LAYER_KERNELS)
+
+
+def layer_forward(x, weight, p, w_index_ci, w_index_co, y_dist, pos, workspace, running_mean, momentum, mean, bias,
+                  out):
+    """snb_layer_forward on 2-D tensors: x [B, CI'], weight [W_CO, W_CI], y_dist / out [B, CO'],
+    pos int32 [B, CO'] or None, workspace any tensor or None, mean [W_CO] or None (None = no mean
+    shift), running_mean [W_CO] or None, bias [W_CO] or None."""
+    B, CI = x.shape
+    CO = y_dist.size(1)
+    nbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    _layer_call("snb_layer_forward", (B, CO, CI), x,
+                x.data_ptr(), weight.data_ptr(), B, CO, CI, float(p), _ptr(w_index_ci), _ptr(w_index_co),
+                weight.size(0), weight.size(1), y_dist.data_ptr(), _ptr(pos), _ptr(workspace), nbytes,
+                _ptr(running_mean), float(momentum), _ptr(mean), _ptr(bias), out.data_ptr())
+
+
+def layer_backward(grad_out, x, weight, y_dist, pos, p, w_index_ci, w_index_co, mean_shift, mean, grad_centred,
+                   grad_bias, grad_x, grad_w):
+    """snb_layer_backward on 2-D tensors (see layer_forward); grad_x [B, CI'] or None, grad_w like
+    weight or None, grad_bias [W_CO] or None; mean [W_CO] and grad_centred [B, CO'] are scratch for
+    the mean-shift part."""
+    B, CO = grad_out.shape
+    CI = x.size(1)
+    _layer_call("snb_layer_backward", (B, CO, CI), grad_out,
+                grad_out.data_ptr(), x.data_ptr(), weight.data_ptr(), _ptr(y_dist), _ptr(pos), B, CO, CI, float(p),
+                _ptr(w_index_ci), _ptr(w_index_co), weight.size(0), weight.size(1), 1 if mean_shift else 0,
+                _ptr(mean), _ptr(grad_centred), _ptr(grad_bias), _ptr(grad_x), _ptr(grad_w))
+
+
+def layer_bound_forward(x, xl, xu, weight, running_mean, bias, y, yl, yu):
+    """snb_layer_bound_forward on 2-D tensors; x / y or xl, xu / yl, yu may be None."""
+    some = x if x is not None else xl
+    B, CI = some.shape
+    CO = weight.size(0)
+    _layer_call("snb_layer_bound_forward", (B, CO, CI), some,
+                _ptr(x), _ptr(xl), _ptr(xu), weight.data_ptr(), B, CO, CI, _ptr(running_mean), _ptr(bias), _ptr(y),
+                _ptr(yl), _ptr(yu))
+
+
+def input_box(x, eps, down, up, xl, xu):
+    """xl = max(x - eps, down), xu = min(x + eps, up) with Python-number bounds."""
+    _layer_call("snb_input_box", (x.numel(),), x, x.data_ptr(), float(eps), float(down), float(up), x.numel(),
+                xl.data_ptr(), xu.data_ptr())
+
+
+def margin_loss(d, targets, eps, clip, lam, scale, margin, row_loss, loss, grad_d):
+    """snb_margin_loss: d [B, K] fp32, targets [B] int64; margin [B, K] / grad_d [B, K] optional."""
+    B, K = d.shape
+    _layer_call("snb_margin_loss", (B, K), d, d.data_ptr(), targets.data_ptr(), B, K, float(eps), float(clip),
+                float(lam), float(scale), _ptr(margin), row_loss.data_ptr(), loss.data_ptr(), _ptr(grad_d))
+
+
+def certified_fraction(yl, yu, targets, row_flag, fraction):
+    """snb_certified_fraction: bounds [B, K] fp32, targets [B] int64 -> fraction (0-d / 1-element)."""
+    B, K = yl.shape
+    _layer_call("snb_certified_fraction", (B, K), yl, yl.data_ptr(), yu.data_ptr(), targets.data_ptr(), B, K,
+                row_flag.data_ptr(), fraction.data_ptr())
+
+
 def install():
     """Registers this module under the name the reference's operator layer imports."""
     sys.modules["norm_dist_cuda"] = sys.modules[__name__]

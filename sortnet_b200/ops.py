@@ -8,6 +8,11 @@ core/norm_dist.py, implemented on the sm_100a kernels.
     bound_inf_dist(x_lower, x_upper, weight, groups=1, use_custom_cuda_func=True, tag=None) (:246)
     NormDistF (:6), NormDistDropoutF (:54), SortNeuronF (:102), BoundInfDistF (:136)
 
+Beyond the reference's names: norm_dist_layer / NormDistLayerF (distance + mean shift + bias of one
+fully connected layer in one call per direction) and margin_loss / MarginLossF (the model's margin
+and the mixture loss with their gradient), which `sortnet_b200.layers` uses to keep the host time
+of a step below its GPU time at small per-GPU batches.
+
 Tensors are (B, C, HW) contiguous fp32 CUDA, weight is (CO, CI / groups), index lists are int32
 (S, groups, count) or None.  The reference's `use_custom_cuda_func=False` switch selected a
 slow PyTorch path; there is none here, so asking for it raises.
@@ -166,6 +171,118 @@ class BoundInfDistF(torch.autograd.Function):
         elif need_l and need_u:
             _C.bound_inf_dist_backward_input(*grads, grad_xl, grad_xu, ctx.group)
         return (grad_xl if need_l else None), (grad_xu if need_u else None), grad_w, None, None, None
+
+
+def _sink_target(param, need):
+    """Where the gradient of `param` is written: (tensor to hand to the kernel, add_after, sink)."""
+    if not need:
+        return None, False, None
+    sink = getattr(param, "grad_sink", None)
+    add_after = sink is not None and getattr(param, "grad_sink_written", False)
+    target = sink if (sink is not None and not add_after) else torch.empty_like(param)
+    return target, add_after, sink
+
+
+def _sink_finish(param, target, add_after, sink):
+    """Returns what autograd gets for `param` (None when the gradient went into its sink)."""
+    if sink is None:
+        return target
+    if add_after:
+        sink.add_(target)
+    param.grad_sink_written = True
+    return None
+
+
+class NormDistLayerF(torch.autograd.Function):
+    """One fully connected norm-distance layer in one call per direction: distance (any p, optional
+    index lists), training-mode mean shift (batch mean per channel over the rows that kept it,
+    momentum update of `running_mean`, gradient through the mean) and bias.  2-D tensors:
+    x [B, CI'], weight [W_CO, W_CI], result [B, CO'].  The arithmetic is that of
+    norm_dist_dropout -> MeanShiftDropout -> bias add (core/models/norm_dist.py:85-103), enqueued
+    by snb_layer_forward / snb_layer_backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, momentum, ci, co, p, shift, record):
+        x = x.contiguous()
+        B = x.size(0)
+        n_out = weight.size(0) if co is None else co.size(-1)
+        inf = math.isinf(p)
+        dev = x.device
+        y = torch.empty(B, n_out, device=dev, dtype=torch.float32)
+        pos = ws = mean = None
+        if inf and (record or ci is not None or co is not None):
+            pos = torch.empty(B, n_out, device=dev, dtype=torch.int32)
+            ws = torch.empty(B * n_out, device=dev, dtype=torch.int64)
+        elif not inf and p > 10:
+            ws = torch.empty(B * n_out, device=dev, dtype=torch.float32)
+        if shift:
+            mean = torch.empty(weight.size(0), device=dev, dtype=torch.float32)
+        # the backward of a finite p needs the distances themselves; for p = inf they may be shifted in place
+        out = y if (inf or not record or (not shift and bias is None)) else torch.empty_like(y)
+        _C.layer_forward(x, weight, p, ci, co, y, pos, ws, running_mean if shift else None, momentum, mean,
+                         bias, out)
+        ctx.p, ctx.shift, ctx.masks = p, shift, (ci, co)
+        ctx.has_bias = bias is not None
+        if record:
+            ctx.save_for_backward(x, weight, pos if inf else y, bias)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, third, bias = ctx.saved_tensors
+        ci, co = ctx.masks
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_b = ctx.has_bias and ctx.needs_input_grad[2]
+        grad_out = grad_out.contiguous()
+        inf = math.isinf(ctx.p)
+        dev = grad_out.device
+        grad_x = torch.empty_like(x) if (need_x or need_w) else None
+        gw, gw_add, gw_sink = _sink_target(weight, need_w)
+        gb, gb_add, gb_sink = _sink_target(bias, need_b)
+        mean = centred = None
+        if ctx.shift:
+            mean = torch.empty(weight.size(0), device=dev, dtype=torch.float32)
+            centred = torch.empty_like(grad_out)
+        _C.layer_backward(grad_out, x, weight, None if inf else third, third if inf else None, ctx.p, ci, co,
+                          ctx.shift, mean, centred, gb, grad_x, gw)
+        return (grad_x if need_x else None, _sink_finish(weight, gw, gw_add, gw_sink) if need_w else None,
+                _sink_finish(bias, gb, gb_add, gb_sink) if need_b else None, None, None, None, None, None, None,
+                None)
+
+
+class MarginLossF(torch.autograd.Function):
+    """Margin of the training forward plus the `mixture` loss on the head's outputs d [B, K]
+    (ell_inf_models.py:45-50 with lower = d - eps, upper = d + eps; main.py:357-364): forward and
+    gradient in one kernel (snb_margin_loss).  Returns the scalar loss."""
+
+    @staticmethod
+    def forward(ctx, d, targets, eps, clip, lam, scale, need):
+        d = d.contiguous()
+        B = d.size(0)
+        loss = torch.empty((), device=d.device, dtype=torch.float32)
+        rows = torch.empty(B, device=d.device, dtype=torch.float32)
+        grad = torch.empty_like(d) if need else None
+        _C.margin_loss(d, targets.contiguous(), eps, clip, lam, scale, None, rows, loss, grad)
+        if need:
+            ctx.save_for_backward(grad)
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        (grad,) = ctx.saved_tensors
+        return grad * grad_loss, None, None, None, None, None, None
+
+
+def norm_dist_layer(x, weight, bias, p, w_index_ci=None, w_index_co=None, running_mean=None, momentum=0.1):
+    """y = (||x - w||_p - batch mean) + bias for 2-D x [B, CI'], training-mode statistics; the mean
+    shift is applied when `running_mean` is given (it is updated in place with `momentum`)."""
+    shift = running_mean is not None
+    record = _wants_grad(x, weight) or (bias is not None and _wants_grad(bias))
+    return NormDistLayerF.apply(x, weight, bias, running_mean, momentum, w_index_ci, w_index_co, p, shift, record)
+
+
+def margin_loss(d, targets, eps, clip=1.0, lam=0.1, scale=1.0):
+    return MarginLossF.apply(d, targets, eps, clip, lam, scale, _wants_grad(d))
 
 
 def norm_dist(input, weight, p, groups=1, use_custom_cuda_func=True, tag=None):
