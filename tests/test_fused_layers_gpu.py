@@ -94,7 +94,9 @@ def test_margin_loss_kernel_value_margin_and_gradient(B, K, eps):
         assert rel(d.grad.cpu().numpy(), dr.grad.cpu().numpy()) < 1e-5
         m = torch.empty(B, K, device="cuda")
         C.margin_loss(d0, t, eps, 1.0, 0.1, scale, m, torch.empty(B, device="cuda"), torch.empty((), device="cuda"), None)
-        assert torch.equal(m, margin.detach())
+        # PyTorch divides by the scalar 2 * eps its own way (a reciprocal held in higher precision):
+        # the last bit may differ
+        assert rel(m.cpu().numpy(), margin.detach().cpu().numpy()) < 5e-7
 
 
 @pytest.mark.parametrize("keep", [1.0, 0.8])
