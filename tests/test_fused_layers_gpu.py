@@ -148,4 +148,4 @@ def test_input_box_and_certified_fraction_kernels():
     C.certified_fraction(yl, yu, t, torch.empty(300, device="cuda"), frac)
     margin = (-yl) - torch.gather(-yu, 1, t.view(-1, 1))
     want = (margin.scatter(1, t.view(-1, 1), float("-inf")).max(dim=1)[0] < 0).float().mean()
-    assert float(frac) == float(want) and 0.0 < float(want) < 1.0
+    assert round(float(frac) * 300) == round(float(want) * 300) and 0.0 < float(want) < 1.0
