@@ -121,7 +121,7 @@ def test_certified_margin_agrees_with_the_evaluation_forward(keep):
         _, margin = model(x, targets=t, eps=eps, up=up, down=down)
     want = (margin.scatter(1, t.view(-1, 1), float("-inf")).max(dim=1)[0] < 0).float().mean()
     got = model.certified_margin(x, t, eps, up, down)
-    assert float(got) == float(want)
+    assert round(float(got) * 96) == round(float(want) * 96)         # the same rows are certified
     assert not model.training
     plain = model.certified_margin(x, t, eps, up, down, sort_eval=False)
     if keep == 1.0:
