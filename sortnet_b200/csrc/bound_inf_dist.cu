@@ -369,13 +369,22 @@ extern "C" int snb_bound_inf_dist_forward_nograd(const float* xl, const float* x
     BoundParams p{xl, xu, w, yl, yu, nullptr, nullptr, B, CO, CI, 0, 0, 0};
     const bool vec = (CI % 4 == 0) && aligned16(xl) && aligned16(xu) && aligned16(w);
     cudaStream_t st = (cudaStream_t)stream;
-    const long big = (long)((B + 127) / 128) * ((CO + 127) / 128);
-    if (big >= sm_count() / 2 && tma_enabled()) {
+    // Tile shape by measurement on B200 (5120 x 5120 layers, 32..1024 rows): 64 x 256 output tiles are
+    // the fastest from 64 rows up (0.33 / 0.62 / 0.92 / 1.22 / 2.40 ms at 64 / 128 / 192 / 256 / 512 rows;
+    // 128-row tiles waste the padding rows below 256 and are 1 % slower above), 32 x 256 for a single
+    // sub-batch.  Narrow layers (a head with few outputs) keep tall tiles: the TMA-staged 128 x 128
+    // kernel when the rows fill it, else 32 x 128.
+    if (CO > 128) {
+        if (B > 32) SNB_CUDA(vec ? launch_bound<2, 4, true>(p, st) : launch_bound<2, 4, false>(p, st));
+        else SNB_CUDA(vec ? launch_bound<1, 4, true>(p, st) : launch_bound<1, 4, false>(p, st));
+        return SNB_OK;
+    }
+    if (B >= 128 && tma_enabled()) {
         cudaError_t e = bound_forward_tma(xl, xu, w, yl, yu, B, CO, CI, st);
         if (e == cudaSuccess) return SNB_OK;
         if (e != cudaErrorNotSupported) SNB_CUDA(e);
     }
-    if (big >= sm_count() / 2) {
+    if (B >= 128) {
         SNB_CUDA(vec ? launch_bound<4, 2, true>(p, st) : launch_bound<4, 2, false>(p, st));
     } else {
         SNB_CUDA(vec ? launch_bound<1, 2, true>(p, st) : launch_bound<1, 2, false>(p, st));

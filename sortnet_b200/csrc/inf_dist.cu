@@ -375,8 +375,9 @@ static cudaError_t dispatch_fwd(const InfFwdParams& q, unsigned long long* keys,
                                : launch_sk<1, 2, MODE_GATHER, TRACK>(p, split, st);
     }
     const bool vec = (q.CI % 4 == 0) && (q.W_CI % 4 == 0) && aligned16(q.x) && aligned16(q.w);
-    const long big = (long)((q.B + 63) / 64) * ((q.CO + 127) / 128);
-    if (big >= sms)
+    // 64-row tiles from two sub-batches up (measured: never slower than 32-row tiles, 1-2 % faster at
+    // 64..256 rows); the stream-K split keeps every SM busy whatever the tile count
+    if (q.B > 32)
         return vec ? launch_sk<2, 2, MODE_VEC, TRACK>(p, split, st) : launch_sk<2, 2, MODE_SCALAR, TRACK>(p, split, st);
     return vec ? launch_sk<1, 2, MODE_VEC, TRACK>(p, split, st) : launch_sk<1, 2, MODE_SCALAR, TRACK>(p, split, st);
 }
