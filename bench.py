@@ -733,6 +733,10 @@ def run_gpu_arm(args):
     job.opt.check()
     if not math.isfinite(sink):
         raise SystemExit("the step produced a non-finite loss")
+    # a bounded device-side wait (the mbarrier waits of the TMA-staged kernel) that gave up would have
+    # left partly written bounds: read the library's flag where results are read anyway
+    if _lib.load().snb_device_wait_failed() != 0:
+        raise SystemExit("a bounded device-side wait gave up during the run (snb_device_wait_failed)")
     ms, ms_e2e = max_over_ranks([ms, ms_e2e], dev, world)
 
     # ---- a short separate pass with an event pair around every entry-point call ---------
@@ -781,7 +785,7 @@ def run_gpu_arm(args):
                 "efficiency_vs_n1": round(ms_solo / (world * ms_strong), 4),
                 "exchange_ms_exposed": round(ms_strong - ms_strong_compute, 3)}
             job.opt.check()
-    if world == 8 and not args.no_extras:
+    if (world == 8 or (args.configs4 and world > 1)) and not args.no_extras:
         job.release()
         cfg = CONFIGS[4]
         big = Job(cfg, dev, world, rank, exchange=exchange)
@@ -862,6 +866,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="copies", choices=["copies", "fused", "nccl"],
                     help="gradient exchange at N > 1 (default: overlapped device-to-device copies)")
+    ap.add_argument("--configs4", action="store_true", help="run the configs[4] block (width 10240, 128 rows per GPU) at "
+                                                           "this N > 1 as well; by default it runs at N = 8 only")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary blocks (other configurations, finite p, "
                                                               "GPU comparator)")

@@ -282,7 +282,12 @@ constexpr int LPB_JT = 32;
 // are two vector loads (all lanes of a warp that share tb read the same words: broadcast)
 constexpr int LPB_GLD = 36;
 
-template <int IP, int NT>
+// FINE (general exponent only): the two warp votes per 16-term batch ("all terms negligible",
+// "some ratio near 1 -> accurate log2 series").  They pay from p - 1 >= 40: below that no term is
+// negligible and the hardware log2's absolute error of 2^-22, multiplied by p - 1, stays under
+// 7e-6 of a term; without the votes nothing separates the batches and the compiler overlaps
+// their log2 / exp2 chains.
+template <int IP, int NT, bool FINE>
 __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdParams p) {
     constexpr int LPB_WLD = NT + 4;  // floats per W-tile row (+4: keeps 16-byte alignment, shifts banks)
     extern __shared__ __align__(16) float smem[];
@@ -416,11 +421,13 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
                             u[ii][k] = (xv[4 * h + ii][k] - wv[k]) * ry;
                             lg[ii][k] = lg2_approx(fabsf(u[ii][k]));
                         }
+                        if (FINE) {
 #pragma unroll
-                        for (int k = 0; k < 4; k += 2) big = max3abs(big, u[ii][k], u[ii][k + 1]);
+                            for (int k = 0; k < 4; k += 2) big = max3abs(big, u[ii][k], u[ii][k + 1]);
+                        }
                     }
-                    if (use_skip && __all_sync(0xffffffffu, big < skip_below)) continue;
-                    if (__any_sync(0xffffffffu, big >= 0.875f)) {
+                    if (FINE && use_skip && __all_sync(0xffffffffu, big < skip_below)) continue;
+                    if (FINE && __any_sync(0xffffffffu, big >= 0.875f)) {
 #pragma unroll
                         for (int ii = 0; ii < 4; ii++)
 #pragma unroll
@@ -442,17 +449,16 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
                 }
             }
             if (p.gw) {
-#pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    gwp[k] += __shfl_xor_sync(0xffffffffu, gwp[k], 1);
-                    gwp[k] += __shfl_xor_sync(0xffffffffu, gwp[k], 2);
-                }
-                // after the butterfly every lane holds all four column sums; lane tb sends column
-                // tb, so the warp issues ONE reduction instruction per output row covering 32
-                // neighbouring kept columns (4-5 sectors) instead of four instructions from 8 lanes
+                // Sum over the four lanes (tb = 0..3) that hold the same four columns, ending with
+                // column tb on lane tb: each lane passes on the half it does not keep (3 shuffles
+                // instead of 8).  The warp then issues ONE reduction instruction per output row
+                // covering 32 neighbouring kept columns (4-5 sectors).
                 {
+                    const bool hi2 = tb & 2, hi1 = tb & 1;
+                    const float a0 = (hi2 ? gwp[2] : gwp[0]) + __shfl_xor_sync(0xffffffffu, hi2 ? gwp[0] : gwp[2], 2);
+                    const float a1 = (hi2 ? gwp[3] : gwp[1]) + __shfl_xor_sync(0xffffffffu, hi2 ? gwp[1] : gwp[3], 2);
+                    const float v = (hi1 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, hi1 ? a0 : a1, 1);
                     const int row = co_s ? co_s[j0 + jj] : j0 + jj;
-                    const float v = tb == 0 ? gwp[0] : tb == 1 ? gwp[1] : tb == 2 ? gwp[2] : gwp[3];
                     if (mycol >= 0) atomicAdd(p.gw + (size_t)row * p.W_CI + mycol, -v);
                 }
             }
@@ -477,7 +483,7 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
 
 // One CTA per resident slot (SMs x CTAs per SM by the occupancy calculator), each with an equal
 // share of the work units; grad_x is zero-filled first because partial ranges add into it.
-template <int IP>
+template <int IP, bool FINE = true>
 static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
     constexpr int NT = 128;
     constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * LPB_GLD) * (int)sizeof(float);
@@ -486,7 +492,7 @@ static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
     cudaGetDevice(&dev);
     std::atomic<int>& slot = cached[dev & 63];
     int cps = slot.load(std::memory_order_acquire);
-    auto kern = lp_bwd_kernel<IP, NT>;
+    auto kern = lp_bwd_kernel<IP, NT, FINE>;
     if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         int occ = 0;
@@ -640,7 +646,10 @@ static int lp_backward(const float* g, const float* x, const float* w, const flo
         case 5: SNB_CUDA(launch_lp_bwd<5>(q, st)); break;
         case 6: SNB_CUDA(launch_lp_bwd<6>(q, st)); break;
         case 7: SNB_CUDA(launch_lp_bwd<7>(q, st)); break;
-        default: SNB_CUDA(launch_lp_bwd<-1>(q, st)); break;
+        default:
+            if (p - 1.0f >= 40.0f) SNB_CUDA((launch_lp_bwd<-1, true>(q, st)));
+            else SNB_CUDA((launch_lp_bwd<-1, false>(q, st)));
+            break;
     }
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
