@@ -55,10 +55,10 @@ HEADLINE = CONFIGS[1]
 ADAM = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (bound_fwd_tma_kernel_512x5120x5120.md; inf_fwd_sk_kernel_masked_512x4619x4596.md,
+# profiles/ (bound_fwd_kernel_64x256_512x5120x5120.md; inf_fwd_sk_kernel_masked_512x4619x4596.md,
 # forward + resolve kernels), at the shapes of the widest layers of the headline workload.
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "snb_bound_inf_dist_forward_nograd": 202.7e6,
+    "snb_bound_inf_dist_forward_nograd": 302.8e6,
     "snb_inf_dist_forward_ws": 262.2e6,
 }
 
@@ -392,11 +392,18 @@ def kernel_stats(timeline, entry):
 
 
 def profiled_pass(job, steps, **kw):
-    """A few steps with a CUDA-event pair around every entry-point call: {(entry, shape): [ms]}."""
-    from sortnet_b200 import norm_dist_cuda as C
-    C.start_profile()
-    job.run(steps, **kw)
-    return C.stop_profile()
+    """A few steps with a CUDA-event pair around every entry-point call: {(entry, shape): [ms]}.
+    The layers are run operator by operator here (the same kernels in the same order as the
+    one-call-per-layer path of the headline regions), so that every kernel gets its own events."""
+    from sortnet_b200 import layers, norm_dist_cuda as C
+    layers.FUSED_LAYERS = False
+    try:
+        job.run(1, **kw)                      # first use of the operator-by-operator path, untimed
+        C.start_profile()
+        job.run(steps, **kw)
+        return C.stop_profile()
+    finally:
+        layers.FUSED_LAYERS = True
 
 
 def roofline_blocks(timeline, peak_gflops):
@@ -821,8 +828,9 @@ def run_gpu_arm(args):
             line.update({"roofline": dominant, "roofline_linf_forward": roofs.get("snb_inf_dist_forward_ws"),
                          "roofline_linf_point_forward": roofs.get("snb_inf_dist_forward_nograd"),
                          "kernel_time_share": shares, "kernel_ms_per_step": round(total_kernel_ms / 3, 3),
-                         "kernel_time_source": "3 extra steps with a CUDA-event pair around every entry-point call; the "
-                                               "headline regions run without them"})
+                         "kernel_time_source": "3 extra steps, run operator by operator with a CUDA-event pair around "
+                                               "every entry-point call; the headline regions run one library call "
+                                               "per layer without those events"})
         line.update(extra)
         if world == 1 and not args.no_extras:
             line["roofline_hbm"] = hbm_block(job)
