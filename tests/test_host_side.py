@@ -116,3 +116,14 @@ def test_model_state_dict_keys_match_the_reference_layout():
     assert keys == {"fc_dist.0.weight", "fc_dist.0.mean_shift.running_mean", "fc_dist.1.weight",
                     "fc_dist.1.mean_shift.running_mean", "fc_dist.2.weight",
                     "fc_dist.2.mean_shift.running_mean", "fc_dist.3.weight", "fc_dist.3.bias"}
+
+
+def test_shard_bounds_tile_the_flat_buffer():
+    from sortnet_b200.optim import shard_bounds
+    for numel in (4, 8, 120, 4096, 120644 // 4 * 4):
+        for world in (1, 2, 3, 4, 8):
+            edges = [shard_bounds(numel, world, r) for r in range(world)]
+            assert edges[0][0] == 0 and edges[-1][1] == numel
+            for (lo, hi), (lo2, _) in zip(edges, edges[1:]):
+                assert hi == lo2 and lo <= hi
+            assert all(lo % 4 == 0 and hi % 4 == 0 for lo, hi in edges)

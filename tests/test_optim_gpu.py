@@ -98,3 +98,49 @@ def test_reduce_step_equals_plain_step_on_the_summed_gradient(parts):
                                      *args, st) == 3
     assert lib.snb_adamw_reduce_step(w.data_ptr(), w_dst.data_ptr(), ptrs, parts, m2.data_ptr(), v2.data_ptr(), n + 1,
                                      *args, st) == 2
+
+
+def test_gradient_sinks_accumulate_and_unreached_parameters_get_zero():
+    """Two backwards before one step add up in the sink (like autograd's .grad); a parameter that no
+    backward reached since the last step has a zero gradient, not the previous step's."""
+    from sortnet_b200.layers import SortMLPModel
+    from sortnet_b200.optim import FlatAdamW
+    torch.manual_seed(1)
+    model = SortMLPModel(depth=3, width=64, input_dim=(1, 4, 4), num_classes=5, dropout=1.0).cuda()
+    ref = copy.deepcopy(model)
+    opt = FlatAdamW(model, lr=0.01)
+    x1, x2 = torch.rand(64, 1, 4, 4, device="cuda"), torch.rand(64, 1, 4, 4, device="cuda")
+    t = torch.randint(0, 5, (64,), device="cuda")
+    opt.zero_grad()
+    loss_of(model.train(), x1, t, None).backward()
+    loss_of(model.train(), x2, t, None).backward()
+    opt.gather_grads()
+    loss_of(ref.train(), x1, t, None).backward()
+    loss_of(ref.train(), x2, t, None).backward()
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        assert (p.grad_sink - q.grad).abs().max() <= 2e-5 * max(q.grad.abs().max().item(), 1e-12), n
+    opt.step()
+    # next step: only the head is used (the hidden layers are bypassed), their gradient must be zero
+    before = [p.detach().clone() for p in model.parameters()]
+    opt.zero_grad()
+    head = model.fc_dist[-1]
+    h = torch.rand(64, head.in_features, device="cuda")
+    out, _, _ = head(h)
+    out.sum().backward()
+    opt.gather_grads()
+    opt._prepare_grads()
+    for n, p in model.named_parameters():
+        if not n.startswith("fc_dist.2."):
+            assert float(p.grad_sink.abs().max()) == 0.0, n
+    assert float(head.weight.grad_sink.abs().max()) > 0.0
+    del before
+
+
+def test_gradient_all_reduce_refuses_parameters_with_sinks():
+    from sortnet_b200.dist import GradientAllReduce
+    from sortnet_b200.layers import SortMLPModel
+    from sortnet_b200.optim import FlatAdamW
+    model = SortMLPModel(depth=3, width=32, input_dim=(1, 4, 4), num_classes=5, dropout=1.0).cuda()
+    FlatAdamW(model)
+    with pytest.raises(ValueError, match="FlatAdamW"):
+        GradientAllReduce(model.parameters())
