@@ -373,6 +373,10 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
             // integer exponents: g * (|t| / y)^IP = (g / y^IP) * |t|^IP, so the division by y is
             // folded into g once per (row, output) instead of once per term
             if (IP >= 0) gt[o] *= pow_abs<IP>(ry, 0.f);
+            // large general exponents: 1 / y = ry * (1 + e) with e = 1 - y * ry known exactly (one
+            // fma); (1 + e)^(p-1) = 1 + (p-1) e to first order goes into g, so that the rounding of
+            // the reciprocal is not amplified by the exponent in every term
+            if (IP < 0 && FINE) gt[o] = fmaf(gt[o], p.pm1 * fmaf(-v, ry, 1.0f), gt[o]);
         }
         __syncthreads();
         const int j0 = t * LPB_JT;
@@ -433,7 +437,15 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
 #pragma unroll
                             for (int k = 0; k < 4; k++) {
                                 const float a = fabsf(u[ii][k]);
-                                if (near_one(a)) lg[ii][k] = log2_series(a);
+                                if (near_one(a)) {
+                                    // the product t * ry was rounded: its exact remainder (one fma),
+                                    // relative to the ratio (1 / a = 2 - a near 1), corrects the logarithm,
+                                    // which the exponent would otherwise amplify by p - 1
+                                    const float ry = yp[4 * h + ii];
+                                    const float rem = fmaf(xv[4 * h + ii][k] - wv[k], ry, -u[ii][k]);
+                                    const float corr = copysignf(rem, rem * u[ii][k]) * (2.0f - a);
+                                    lg[ii][k] = fmaf(corr, 1.4426950408889634f, log2_series(a));
+                                }
                             }
                     }
 #pragma unroll
