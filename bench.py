@@ -230,13 +230,14 @@ class Job:
         self.up, self.down = 1.0, 0.0           # the box is clipped to the pixel range [0, 1]
         self.pool = pool
 
-    def bound_pass(self, x, t):
+    def bound_pass(self, x, t, after_layer=None):
         """The l-inf interval-bound forward of the whole net (point value + bounds, running means
         subtracted, certified fraction): the plain l-inf distance in every layer, see
         SortMLPModel.certified_margin(sort_eval=False)."""
         import torch
         with torch.no_grad():
-            return self.model.certified_margin(x, t, self.cfg["eps"], self.up, self.down, sort_eval=False)
+            return self.model.certified_margin(x, t, self.cfg["eps"], self.up, self.down, sort_eval=False,
+                                               after_layer=after_layer)
 
     def step(self, x, t, update=True, bounds=True):
         model, opt = self.model, self.opt
@@ -250,9 +251,12 @@ class Job:
             if bounds:
                 cert = self.bound_pass(x, t)
         elif opt.overlap:
-            opt.begin_exchange()              # side stream: barrier, copies, the shard's update, copies, barrier
+            opt.begin_exchange()              # side stream: barrier, pulls of the gradient shards
             if bounds:
-                cert = self.bound_pass(x, t)  # reads the pre-update weights
+                # reads the pre-update weights; after the third layer the shard's update runs on this
+                # stream (the pulls have landed by then), the pushes and the closing barrier run on
+                # the side stream beside the remaining layers
+                cert = self.bound_pass(x, t, after_layer=lambda k: opt.apply_update() if k == 2 else None)
             opt.end_exchange()
         else:
             # same order as the overlapped path: the bound pass reads the pre-update weights
@@ -665,8 +669,8 @@ def run_gpu_arm(args):
         job = Job(HEADLINE, dev, world, rank, exchange=exchange)
     exchange_text = {
         "none": "none (single GPU)",
-        "copies": "device-to-device copies over NVLink (reduce-scatter, all-gather) + local sum/AdamW kernel, all beside "
-                  "the bound pass, ordered by bounded peer barriers",
+        "copies": "device-to-device copies over NVLink (reduce-scatter, all-gather) beside the bound pass, the shard's "
+                  "sum/AdamW kernel between two of its layers, ordered by bounded peer barriers",
         "fused": "fused reduce-scatter + AdamW + all-gather kernel over NVLink peer memory",
         "nccl": "one flat NCCL all-reduce + local fused AdamW"}[exchange]
     B = job.B

@@ -44,25 +44,32 @@ struct GradParts {
     const float4* g[ADAMW_MAX_PARTS];
 };
 
-// The same update with the gradient given as `parts` partial buffers (summed in index order) and
+// The same update with the gradient given as PARTS partial buffers (summed in index order) and
 // the new values written to a second parameter buffer: the local half of a data-parallel step
-// whose reduce-scatter and all-gather are plain device-to-device copies.
+// whose reduce-scatter and all-gather are plain device-to-device copies.  PARTS is a template
+// parameter so that the part pointers are compile-time-indexed kernel parameters (a run-time index
+// sends the pointer table to local memory and serialises the loads behind it: 0.72 ms instead of
+// 0.2 ms for 30 M values in four parts); all loads of an element are issued before the first use.
+template <int PARTS>
 __global__ void __launch_bounds__(256) adamw_reduce_kernel(const float4* __restrict__ w_src, float4* __restrict__ w_dst,
-                                                           const GradParts parts, int n_parts, float4* __restrict__ m,
+                                                           const GradParts parts, float4* __restrict__ m,
                                                            float4* __restrict__ v, size_t n4, float decay, float b1,
                                                            float b2, float step_size, float inv_sqrt_bc2, float eps,
                                                            float grad_scale) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        float4 gv = parts.g[0][i];
-        for (int r = 1; r < n_parts; r++) {
-            const float4 t = parts.g[r][i];
-            gv.x += t.x;
-            gv.y += t.y;
-            gv.z += t.z;
-            gv.w += t.w;
-        }
+        float4 t[PARTS];
+#pragma unroll
+        for (int r = 0; r < PARTS; r++) t[r] = __ldcs(parts.g[r] + i);     // read once: streaming loads
         float4 wv = w_src[i], mv = m[i], vv = v[i];
+        float4 gv = t[0];
+#pragma unroll
+        for (int r = 1; r < PARTS; r++) {
+            gv.x += t[r].x;
+            gv.y += t[r].y;
+            gv.z += t[r].z;
+            gv.w += t[r].w;
+        }
         float* wp = reinterpret_cast<float*>(&wv);
         const float* gp = reinterpret_cast<const float*>(&gv);
         float* mp = reinterpret_cast<float*>(&mv);
@@ -100,10 +107,23 @@ extern "C" int snb_adamw_reduce_step(const float* w_src, float* w_dst, const voi
     }
     const double bc1 = 1.0 - pow((double)beta1, step), bc2 = 1.0 - pow((double)beta2, step);
     const float step_size = (float)(lr / bc1), inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
-    adamw_reduce_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const float4*>(w_src), reinterpret_cast<float4*>(w_dst), gp, parts,
-        reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v), (size_t)n / 4, 1.0f - lr * weight_decay, beta1,
-        beta2, step_size, inv_sqrt_bc2, eps, grad_scale);
+    const int blocks = sm_count() * 8;
+    cudaStream_t st = (cudaStream_t)stream;
+#define SNB_REDUCE_CASE(P)                                                                                          \
+    case P:                                                                                                         \
+        adamw_reduce_kernel<P><<<blocks, 256, 0, st>>>(reinterpret_cast<const float4*>(w_src),                      \
+                                                       reinterpret_cast<float4*>(w_dst), gp, reinterpret_cast<float4*>(m), \
+                                                       reinterpret_cast<float4*>(v), (size_t)n / 4,                 \
+                                                       1.0f - lr * weight_decay, beta1, beta2, step_size,           \
+                                                       inv_sqrt_bc2, eps, grad_scale);                              \
+        break;
+    switch (parts) {
+        SNB_REDUCE_CASE(1) SNB_REDUCE_CASE(2) SNB_REDUCE_CASE(3) SNB_REDUCE_CASE(4) SNB_REDUCE_CASE(5)
+        SNB_REDUCE_CASE(6) SNB_REDUCE_CASE(7) SNB_REDUCE_CASE(8) SNB_REDUCE_CASE(9) SNB_REDUCE_CASE(10)
+        SNB_REDUCE_CASE(11) SNB_REDUCE_CASE(12) SNB_REDUCE_CASE(13) SNB_REDUCE_CASE(14) SNB_REDUCE_CASE(15)
+        SNB_REDUCE_CASE(16)
+    }
+#undef SNB_REDUCE_CASE
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
 }

@@ -411,7 +411,7 @@ class SortMLPModel(nn.Module):
         return masks
 
     @torch.no_grad()
-    def certified_margin(self, x, targets, eps, up, down, sort_eval=None):
+    def certified_margin(self, x, targets, eps, up, down, sort_eval=None, after_layer=None):
         """Evaluation-mode interval-bound pass over the box [x - eps, x + eps] clipped to
         [down, up], running means subtracted.  Returns the fraction of rows whose worst-case
         margin is negative for every wrong class.
@@ -424,7 +424,11 @@ class SortMLPModel(nn.Module):
         every layer, whatever the keep rates: that is the l-inf interval-bound workload
         (bound_inf_dist_cuda.cu), and a certificate only for a network whose keep rates are all 1;
         for a sort-neuron network the number it returns is NOT a certified accuracy, because the
-        sort neuron's output lies below the l-inf distance."""
+        sort neuron's output lies below the l-inf distance.
+
+        after_layer: optional callable(k), called after layer k has been queued; a caller that
+        overlaps other work with this pass (optim.FlatAdamW.apply_update) uses it to place that
+        work between two layers."""
         was_training = self.training
         self.eval()
         if sort_eval is None:
@@ -439,9 +443,11 @@ class SortMLPModel(nn.Module):
             else:
                 lower = torch.maximum(x - eps, torch.as_tensor(down, device=x.device))
                 upper = torch.minimum(x + eps, torch.as_tensor(up, device=x.device))
-            for layer in self.fc_dist:
+            for k, layer in enumerate(self.fc_dist):
                 assert math.isinf(layer.p)
                 x, lower, upper = layer(x, lower, upper, sort_eval=sort_eval and layer.keep_rate != 1.0)
+                if after_layer is not None:
+                    after_layer(k)
             if FUSED_LAYERS and x.is_cuda:
                 frac = torch.empty((), device=x.device, dtype=torch.float32)
                 rows = torch.empty(x.size(0), device=x.device, dtype=torch.float32)

@@ -57,10 +57,12 @@ class FlatAdamW:
 
         overlap=True (with peer_memory): the exchange runs beside other work of the step.
         `begin_exchange()` queues, on a side stream, device-to-device copies of this rank's shard of
-        every peer's gradients (copy engines over NVLink, no SM time), the local sum + AdamW kernel
-        and copies of the updated shard into every peer's *second* parameter buffer;
-        `end_exchange()` makes the main stream wait for them and switches the parameters to that
-        buffer.  Kernels launched in between (the interval-bound pass) keep reading the old values.
+        every peer's gradients (copy engines over NVLink, no SM time); `apply_update()` runs the
+        local sum + AdamW kernel on the caller's stream between two of its kernels and lets the side
+        stream copy the updated shard into every peer's *second* parameter buffer;
+        `end_exchange()` makes the main stream wait for that and switches the parameters to the
+        second buffer.  Kernels launched in between (the interval-bound pass) keep reading the old
+        values.
 
         Ranks are ordered by `snb_peer_barrier` kernels on the exchange's stream.  Their wait is
         bounded by `barrier_timeout_s`: a rank that does not arrive makes its peers' barrier give up
@@ -154,8 +156,10 @@ class FlatAdamW:
         self._recv = {r: torch.empty(shape, device=dev, dtype=torch.float32) for r in peers}
         self._side = torch.cuda.Stream(device=dev)
         self._ready = torch.cuda.Event()
+        self._pulled = torch.cuda.Event()
+        self._updated = torch.cuda.Event()
         self._done = torch.cuda.Event()
-        self._in_flight = False
+        self._in_flight = self._updated_queued = False
 
     def _barrier(self, stream):
         """Enqueues the bounded inter-rank barrier on `stream`; raises at once if it cannot be launched."""
@@ -178,8 +182,14 @@ class FlatAdamW:
                                % (int(self._status[0]) - 1, self._timeout_ns * 1e-9))
 
     def begin_exchange(self):
-        """Queues the gradient exchange and the update of this rank's shard behind everything that
-        is on the current stream now (the backward); returns at once.
+        """Queues the first half of the gradient exchange behind everything that is on the current
+        stream now (the backward) and returns at once: on a side stream, a barrier (every rank's
+        backward has written its gradients) and device-to-device copies of this rank's shard of every
+        peer's gradient buffer.  Copies and barriers take no SM time and were measured not to slow
+        kernels running beside them.
+
+        The shard update itself is a kernel; `apply_update()` runs it on the caller's stream at a
+        point of the caller's choosing, `end_exchange()` does so if the caller did not.
 
         Every launch status is examined before the next operation is queued: a rank that cannot
         launch stops there (pushing nothing, signalling nothing) and raises, and its peers' next
@@ -190,40 +200,68 @@ class FlatAdamW:
         self._prepare_grads()
         self.step_count += 1
         dev = self.flat_grad.device
-        lo, hi, n = self.lo, self.hi, self.hi - self.lo
-        cur, nxt = self._param_bufs[self._cur], self._param_bufs[self._cur ^ 1]
         with torch.cuda.device(dev):
             self._ready.record(torch.cuda.current_stream(dev))
             self._side.wait_event(self._ready)
             with torch.cuda.stream(self._side):
-                # every rank's backward has finished writing its gradients ...
                 self._barrier(self._side)
-                if n > 0:
+                if self.hi > self.lo:
                     for r, src in self._peer_grad.items():
                         self._recv[r].copy_(src, non_blocking=True)
-                    parts = [self.flat_grad[lo:hi] if r == self.rank else self._recv[r] for r in range(self.world)]
-                    ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in parts])
-                    rc = _lib.load().snb_adamw_reduce_step(
-                        cur[lo:hi].data_ptr(), nxt[lo:hi].data_ptr(), ptrs, self.world, self.exp_avg.data_ptr(),
-                        self.exp_avg_sq.data_ptr(), n, float(self.lr), float(self.betas[0]), float(self.betas[1]),
-                        float(self.eps), float(self.weight_decay), self.step_count, 1.0 / self.world,
-                        self._side.cuda_stream)
-                    if rc != 0:
-                        self._failed = "the shard update could not be launched"
-                    _lib.check(rc, "adamw_reduce_step")
-                    _C.launch_count += 1
+                self._pulled.record(self._side)
+        self._grads_consumed()
+        self._in_flight, self._updated_queued = True, False
+
+    def apply_update(self):
+        """Second part of the exchange, on the *current* stream: waits for the pulled gradient
+        shards, runs the sum + AdamW kernel for this rank's shard into the second parameter buffer,
+        and hands over to the side stream, which pushes the shard into every peer's second buffer
+        and closes with a barrier.
+
+        Why not on the side stream as well: the distance kernels are persistent, one CTA per SM with
+        the whole register file and an equal share of the work each, so a kernel that arrives from
+        another stream can only start at a kernel boundary, holds back some CTAs of the next
+        persistent kernel there, and that kernel then ends as late as its last CTA started
+        (measured at 4 GPUs: +0.7 ... 1.3 ms per step for a 0.15 ms update).  On the caller's own
+        stream, between two of its kernels, the update costs its own duration and nothing else.
+        Call it where the pulls have surely landed and enough work follows to cover the pushes (in
+        the benchmark: after the third layer of the bound pass)."""
+        if not self._in_flight or self._updated_queued:
+            return
+        dev = self.flat_grad.device
+        lo, hi, n = self.lo, self.hi, self.hi - self.lo
+        cur, nxt = self._param_bufs[self._cur], self._param_bufs[self._cur ^ 1]
+        with torch.cuda.device(dev):
+            main = torch.cuda.current_stream(dev)
+            main.wait_event(self._pulled)
+            if n > 0:
+                parts = [self.flat_grad[lo:hi] if r == self.rank else self._recv[r] for r in range(self.world)]
+                ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in parts])
+                rc = _lib.load().snb_adamw_reduce_step(
+                    cur[lo:hi].data_ptr(), nxt[lo:hi].data_ptr(), ptrs, self.world, self.exp_avg.data_ptr(),
+                    self.exp_avg_sq.data_ptr(), n, float(self.lr), float(self.betas[0]), float(self.betas[1]),
+                    float(self.eps), float(self.weight_decay), self.step_count, 1.0 / self.world, main.cuda_stream)
+                if rc != 0:
+                    self._failed = "the shard update could not be launched"
+                _lib.check(rc, "adamw_reduce_step")
+                _C.launch_count += 1
+            self._updated.record(main)
+            self._side.wait_event(self._updated)
+            with torch.cuda.stream(self._side):
+                if n > 0:
                     for r, dst in self._peer_param[self._cur ^ 1].items():
                         dst.copy_(nxt[lo:hi], non_blocking=True)
-                # ... and every rank's shard of the new values has landed in this rank's second buffer
+                # every rank's shard of the new values has landed in this rank's second buffer
                 self._barrier(self._side)
                 self._done.record(self._side)
-        self._grads_consumed()
-        self._in_flight = True
+        self._updated_queued = True
 
     def end_exchange(self):
-        """The current stream waits for the exchange; parameters switch to the updated buffer."""
+        """The current stream waits for the exchange (running the update first if `apply_update()`
+        was not called); parameters switch to the updated buffer."""
         if not self._in_flight:
             raise RuntimeError("end_exchange() without begin_exchange()")
+        self.apply_update()
         dev = self.flat_grad.device
         torch.cuda.current_stream(dev).wait_event(self._done)
         self.check()
