@@ -251,12 +251,17 @@ class Job:
             if bounds:
                 cert = self.bound_pass(x, t)
         elif opt.overlap:
-            opt.begin_exchange()              # side stream: barrier, pulls of the gradient shards
+            opt.begin_exchange()              # side stream: "my gradients are complete"
             if bounds:
-                # reads the pre-update weights; after the third layer the shard's update runs on this
-                # stream (the pulls have landed by then), the pushes and the closing barrier run on
-                # the side stream beside the remaining layers
-                cert = self.bound_pass(x, t, after_layer=lambda k: opt.apply_update() if k == 2 else None)
+                # reads the pre-update weights.  After the first layer the side stream pulls the
+                # gradient shards (the peers have signalled by then), after the third the shard's
+                # update runs on this stream, and the pushes run beside the remaining layers.
+                def stage(k):
+                    if k == 0:
+                        opt.start_pulls()
+                    elif k == 2:
+                        opt.apply_update()
+                cert = self.bound_pass(x, t, after_layer=stage)
             opt.end_exchange()
         else:
             # same order as the overlapped path: the bound pass reads the pre-update weights

@@ -359,6 +359,16 @@ int snb_dp_adamw_step(const void* const* grad_ptrs, void* const* param_ptrs, flo
 int snb_peer_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch,
                      unsigned long long timeout_ns, int* status, void* stream);
 
+/* The two halves of snb_peer_barrier as separate stream-ordered operations with the same arguments:
+ * snb_peer_signal stores `epoch` into every peer's flag word for this rank, snb_peer_wait waits
+ * (bounded, as above) until this rank's flag words hold `epoch` or later.  A kernel that waits on
+ * the GPU costs the kernels running beside it about half of the time it waits (measured on B200),
+ * so a caller with work to overlap signals as early and waits as late as its data flow allows: by
+ * then the peers have signalled and the wait returns at once.  No counterpart in the reference. */
+int snb_peer_signal(void* const* flag_ptrs, int rank, int world, unsigned int epoch, void* stream);
+int snb_peer_wait(void* const* flag_ptrs, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
+                  int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

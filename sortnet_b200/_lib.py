@@ -46,6 +46,8 @@ SIGNATURES = {
     "snb_margin_loss": [_P, _P, _I, _I, _F, _F, _F, _F, _P, _P, _P, _P, _P],
     "snb_certified_fraction": [_P, _P, _P, _I, _I, _P, _P, _P],
     "snb_peer_barrier": [_P, _I, _I, ctypes.c_uint, ctypes.c_ulonglong, _P, _P],
+    "snb_peer_signal": [_P, _I, _I, ctypes.c_uint, _P],
+    "snb_peer_wait": [_P, _I, _I, ctypes.c_uint, ctypes.c_ulonglong, _P, _P],
     "snb_check_index_lists": [_P, _I, _I, _I, ctypes.POINTER(ctypes.c_int), _P],
     "snb_probe_fp32": [_P, _I, ctypes.POINTER(ctypes.c_double), _P],
 }

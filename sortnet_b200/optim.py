@@ -159,7 +159,7 @@ class FlatAdamW:
         self._pulled = torch.cuda.Event()
         self._updated = torch.cuda.Event()
         self._done = torch.cuda.Event()
-        self._in_flight = self._updated_queued = False
+        self._in_flight, self._stage = False, 0
 
     def _barrier(self, stream):
         """Enqueues the bounded inter-rank barrier on `stream`; raises at once if it cannot be launched."""
@@ -181,19 +181,43 @@ class FlatAdamW:
             raise RuntimeError("rank %d did not reach the gradient-exchange barrier within %.1f s"
                                % (int(self._status[0]) - 1, self._timeout_ns * 1e-9))
 
-    def begin_exchange(self):
-        """Queues the first half of the gradient exchange behind everything that is on the current
-        stream now (the backward) and returns at once: on a side stream, a barrier (every rank's
-        backward has written its gradients) and device-to-device copies of this rank's shard of every
-        peer's gradient buffer.  Copies and barriers take no SM time and were measured not to slow
-        kernels running beside them.
+    def _signal(self, stream):
+        self._epoch += 1
+        rc = _lib.load().snb_peer_signal(self._flag_ptrs, self.rank, self.world, self._epoch, stream.cuda_stream)
+        if rc != 0:
+            self._failed = "peer signal could not be launched"
+        _lib.check(rc, "peer_signal")
+        _C.launch_count += 1
+        return self._epoch
 
-        The shard update itself is a kernel; `apply_update()` runs it on the caller's stream at a
-        point of the caller's choosing, `end_exchange()` does so if the caller did not.
+    def _wait(self, epoch, stream):
+        rc = _lib.load().snb_peer_wait(self._flag_ptrs, self.rank, self.world, epoch, self._timeout_ns,
+                                       self._status.data_ptr(), stream.cuda_stream)
+        if rc != 0:
+            self._failed = "peer wait could not be launched"
+        _lib.check(rc, "peer_wait")
+        _C.launch_count += 1
+
+    def begin_exchange(self):
+        """Opens the gradient exchange behind everything that is on the current stream now (the
+        backward) and returns at once: the side stream tells every peer that this rank's gradients
+        are complete.  Nothing waits yet.
+
+        The exchange then proceeds in three more stream-ordered stages, each of which the caller may
+        place between two kernels of the work it overlaps with the exchange (the interval-bound pass),
+        and each of which the next stage runs itself if the caller did not:
+          start_pulls()   side stream: wait for the peers' signals, copy this rank's shard of every
+                          peer's gradient buffer (copy engines over NVLink, no SM time);
+          apply_update()  caller's stream: sum + AdamW for the shard into the second parameter
+                          buffer; side stream: copy the shard into every peer's second buffer, signal;
+          end_exchange()  wait for the peers' signals, switch the parameters to the second buffer.
+        Signals are sent as early and waited for as late as the data flow allows: a kernel that
+        waits on the GPU costs the kernels running beside it about half of the time it waits, and
+        by the time of the wait the peers have normally long signalled.
 
         Every launch status is examined before the next operation is queued: a rank that cannot
         launch stops there (pushing nothing, signalling nothing) and raises, and its peers' next
-        barrier runs into its time limit and reports this rank through check()."""
+        wait runs into its time limit and reports this rank through check()."""
         if not self.overlap:
             raise RuntimeError("begin_exchange() needs FlatAdamW(peer_memory=True, overlap=True)")
         self.check()
@@ -203,31 +227,39 @@ class FlatAdamW:
         with torch.cuda.device(dev):
             self._ready.record(torch.cuda.current_stream(dev))
             self._side.wait_event(self._ready)
-            with torch.cuda.stream(self._side):
-                self._barrier(self._side)
-                if self.hi > self.lo:
-                    for r, src in self._peer_grad.items():
-                        self._recv[r].copy_(src, non_blocking=True)
-                self._pulled.record(self._side)
+            self._grads_epoch = self._signal(self._side)
         self._grads_consumed()
-        self._in_flight, self._updated_queued = True, False
+        self._in_flight, self._stage = True, 1
+
+    def start_pulls(self):
+        """Second stage (side stream): every rank's backward has written its gradients -> pull this
+        rank's shard of each peer's gradient buffer."""
+        if not self._in_flight or self._stage != 1:
+            return
+        dev = self.flat_grad.device
+        with torch.cuda.device(dev), torch.cuda.stream(self._side):
+            self._wait(self._grads_epoch, self._side)
+            if self.hi > self.lo:
+                for r, src in self._peer_grad.items():
+                    self._recv[r].copy_(src, non_blocking=True)
+            self._pulled.record(self._side)
+        self._stage = 2
 
     def apply_update(self):
-        """Second part of the exchange, on the *current* stream: waits for the pulled gradient
-        shards, runs the sum + AdamW kernel for this rank's shard into the second parameter buffer,
-        and hands over to the side stream, which pushes the shard into every peer's second buffer
-        and closes with a barrier.
+        """Third stage, on the *current* stream: waits for the pulled gradient shards, runs the sum +
+        AdamW kernel for this rank's shard into the second parameter buffer, and hands over to the
+        side stream, which pushes the shard into every peer's second buffer and signals.
 
         Why not on the side stream as well: the distance kernels are persistent, one CTA per SM with
         the whole register file and an equal share of the work each, so a kernel that arrives from
         another stream can only start at a kernel boundary, holds back some CTAs of the next
-        persistent kernel there, and that kernel then ends as late as its last CTA started
-        (measured at 4 GPUs: +0.7 ... 1.3 ms per step for a 0.15 ms update).  On the caller's own
-        stream, between two of its kernels, the update costs its own duration and nothing else.
-        Call it where the pulls have surely landed and enough work follows to cover the pushes (in
-        the benchmark: after the third layer of the bound pass)."""
-        if not self._in_flight or self._updated_queued:
+        persistent kernel there, and that kernel then ends as late as its last CTA started.  On the
+        caller's own stream, between two of its kernels, the update costs its own duration (0.2 ms
+        for a quarter of 120 M parameters) and nothing else.  Call it where the pulls have surely
+        landed and enough work follows to cover the pushes."""
+        if not self._in_flight or self._stage > 2:
             return
+        self.start_pulls()
         dev = self.flat_grad.device
         lo, hi, n = self.lo, self.hi, self.hi - self.lo
         cur, nxt = self._param_bufs[self._cur], self._param_bufs[self._cur ^ 1]
@@ -251,10 +283,8 @@ class FlatAdamW:
                 if n > 0:
                     for r, dst in self._peer_param[self._cur ^ 1].items():
                         dst.copy_(nxt[lo:hi], non_blocking=True)
-                # every rank's shard of the new values has landed in this rank's second buffer
-                self._barrier(self._side)
-                self._done.record(self._side)
-        self._updated_queued = True
+                self._params_epoch = self._signal(self._side)
+        self._stage = 3
 
     def end_exchange(self):
         """The current stream waits for the exchange (running the update first if `apply_update()`
@@ -263,6 +293,10 @@ class FlatAdamW:
             raise RuntimeError("end_exchange() without begin_exchange()")
         self.apply_update()
         dev = self.flat_grad.device
+        with torch.cuda.device(dev), torch.cuda.stream(self._side):
+            # every rank's shard of the new values has landed in this rank's second buffer
+            self._wait(self._params_epoch, self._side)
+            self._done.record(self._side)
         torch.cuda.current_stream(dev).wait_event(self._done)
         self.check()
         self._cur ^= 1

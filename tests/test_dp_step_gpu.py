@@ -64,7 +64,8 @@ def _worker(rank, world, port, out, overlap=False):
                 # work queued between begin and end still sees the old values
                 # the shard's update runs on this stream: between two layers of the pass on odd steps
                 # (apply_update), at end_exchange() otherwise
-                hook = (lambda k: opt_a.apply_update() if k == 1 else None) if step % 2 else None
+                hook = (lambda k: opt_a.start_pulls() if k == 0 else opt_a.apply_update() if k == 1 else None) \
+                    if step % 2 else None
                 with torch.no_grad():
                     cert = a.certified_margin(x, t, 0.03, torch.ones(1, device=dev), torch.zeros(1, device=dev),
                                               after_layer=hook)
