@@ -148,7 +148,9 @@ class FlatAdamW:
         self._cur = 0
         n = self.hi - self.lo
         shape = (max(n, 0),)
-        peers = [r for r in range(self.world) if r != self.rank]
+        # ring order (rank + 1, rank + 2, ...): at any moment of the pull or push phase every rank is
+        # read by one peer and written by one peer, instead of all ranks converging on rank 0 first
+        peers = [(self.rank + k) % self.world for k in range(1, self.world)]
         # this rank's shard of every peer's gradient buffer / of every peer's parameter buffers
         self._peer_grad = {r: self._hdl_grad.get_buffer(r, shape, torch.float32, self.lo) for r in peers}
         self._peer_param = [{r: h.get_buffer(r, shape, torch.float32, self.lo) for r in peers}
