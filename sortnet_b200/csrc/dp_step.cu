@@ -25,21 +25,28 @@ struct PeerBuffers {
     float4* param[SNB_MAX_PEERS];
 };
 
+// WORLD is a template parameter so that the peer pointers are compile-time-indexed kernel parameters
+// (a run-time index sends the pointer table to local memory and serialises the loads behind it) and
+// all peer loads of an element are in flight together.
+template <int WORLD>
 __global__ void __launch_bounds__(256) dp_adamw_kernel(const PeerBuffers pb, float4* __restrict__ m,
-                                                       float4* __restrict__ v, int rank, int world, size_t lo4,
-                                                       size_t hi4, float decay, float b1, float b2, float step_size,
-                                                       float inv_sqrt_bc2, float eps, float inv_world) {
+                                                       float4* __restrict__ v, const float4* own_param,
+                                                       size_t lo4, size_t hi4, float decay, float b1, float b2,
+                                                       float step_size, float inv_sqrt_bc2, float eps, float inv_world) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = lo4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi4; i += stride) {
+        float4 t[WORLD];
+#pragma unroll
+        for (int r = 0; r < WORLD; r++) t[r] = pb.grad[r][i];
         float4 gs = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < world; r++) {
-            const float4 g = pb.grad[r][i];
-            gs.x += g.x;
-            gs.y += g.y;
-            gs.z += g.z;
-            gs.w += g.w;
+#pragma unroll
+        for (int r = 0; r < WORLD; r++) {
+            gs.x += t[r].x;
+            gs.y += t[r].y;
+            gs.z += t[r].z;
+            gs.w += t[r].w;
         }
-        float4 wv = pb.param[rank][i], mv = m[i - lo4], vv = v[i - lo4];
+        float4 wv = own_param[i], mv = m[i - lo4], vv = v[i - lo4];
         float* wp = reinterpret_cast<float*>(&wv);
         const float* gp = reinterpret_cast<const float*>(&gs);
         float* mp = reinterpret_cast<float*>(&mv);
@@ -54,7 +61,8 @@ __global__ void __launch_bounds__(256) dp_adamw_kernel(const PeerBuffers pb, flo
         }
         m[i - lo4] = mv;
         v[i - lo4] = vv;
-        for (int r = 0; r < world; r++) pb.param[r][i] = wv;
+#pragma unroll
+        for (int r = 0; r < WORLD; r++) pb.param[r][i] = wv;
     }
 }
 
@@ -86,9 +94,20 @@ extern "C" int snb_dp_adamw_step(const void* const* grad_ptrs, void* const* para
     if (hi == lo) return SNB_OK;
     const double bc1 = 1.0 - pow((double)beta1, step), bc2 = 1.0 - pow((double)beta2, step);
     const int blocks = sm_count() * 4;
-    dp_adamw_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
-        pb, reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v), rank, world, (size_t)lo / 4, (size_t)hi / 4,
-        1.0f - lr * weight_decay, beta1, beta2, (float)(lr / bc1), (float)(1.0 / sqrt(bc2)), eps, 1.0f / (float)world);
+    cudaStream_t st = (cudaStream_t)stream;
+#define SNB_DP_CASE(W)                                                                                              \
+    case W:                                                                                                         \
+        dp_adamw_kernel<W><<<blocks, 256, 0, st>>>(pb, reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v),   \
+                                                   pb.param[rank], (size_t)lo / 4, (size_t)hi / 4,                   \
+                                                   1.0f - lr * weight_decay, beta1, beta2, (float)(lr / bc1),        \
+                                                   (float)(1.0 / sqrt(bc2)), eps, 1.0f / (float)world);              \
+        break;
+    switch (world) {
+        SNB_DP_CASE(1) SNB_DP_CASE(2) SNB_DP_CASE(3) SNB_DP_CASE(4) SNB_DP_CASE(5) SNB_DP_CASE(6) SNB_DP_CASE(7)
+        SNB_DP_CASE(8) SNB_DP_CASE(9) SNB_DP_CASE(10) SNB_DP_CASE(11) SNB_DP_CASE(12) SNB_DP_CASE(13)
+        SNB_DP_CASE(14) SNB_DP_CASE(15) SNB_DP_CASE(16)
+    }
+#undef SNB_DP_CASE
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
 }
