@@ -361,6 +361,64 @@ def dp_check(job, dev, world):
             "tolerance": 1e-5, "exchange": job.exchange, "ok": ok}
 
 
+def exchange_timeline(job, dev, world, steps=10):
+    """Where the overlapped exchange touches the bound pass, from CUDA events on this rank's streams
+    over `steps` extra steps: the two parts of the bound pass (before / after the shard's update), the
+    update kernel, and the time the main stream had to wait for the pulled gradients and for the
+    end of the exchange.  All ranks' rows are gathered on rank 0."""
+    import torch
+    import torch.distributed as dist
+    opt = job.opt
+    if not getattr(opt, "overlap", False):
+        return None
+    new_event = lambda: torch.cuda.Event(enable_timing=True)
+    rows = []
+    begin0, apply0, end0 = opt.begin_exchange, opt.apply_update, opt.end_exchange
+
+    def begin():
+        e = new_event()
+        e.record()
+        rows.append({"begin": e})
+        begin0()
+
+    def apply():
+        if opt._stage > 2:
+            return
+        opt.start_pulls()
+        main = torch.cuda.current_stream(dev)
+        a, b, c = new_event(), new_event(), new_event()
+        a.record()
+        main.wait_event(opt._pulled)
+        b.record()
+        apply0()
+        c.record()
+        rows[-1].update(a=a, b=b, c=c)
+
+    def end():
+        a, b = new_event(), new_event()
+        a.record()
+        end0()
+        b.record()
+        rows[-1].update(e0=a, e1=b)
+
+    opt.begin_exchange, opt.apply_update, opt.end_exchange = begin, apply, end
+    try:
+        job.run(steps + 2)
+        torch.cuda.synchronize()
+    finally:
+        opt.begin_exchange, opt.apply_update, opt.end_exchange = begin0, apply0, end0
+    keep = rows[2:]
+    mean = lambda f: sum(f(r) for r in keep) / len(keep)
+    mine = torch.tensor([mean(lambda r: r["begin"].elapsed_time(r["a"])), mean(lambda r: r["a"].elapsed_time(r["b"])),
+                         mean(lambda r: r["b"].elapsed_time(r["c"])), mean(lambda r: r["c"].elapsed_time(r["e0"])),
+                         mean(lambda r: r["e0"].elapsed_time(r["e1"]))], device=dev, dtype=torch.float64)
+    every = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    names = ("bound_pass_before_update_ms", "wait_for_pulls_ms", "update_kernel_ms", "bound_pass_after_update_ms",
+             "wait_at_end_ms")
+    return [{k: round(float(v), 3) for k, v in zip(names, t)} for t in every]
+
+
 def fp32_peak_gflops(dev):
     """FP32 CUDA-core peak of this GPU, measured now with a register-only FMA chain (2 flops per FMA)."""
     import torch
@@ -765,6 +823,7 @@ def run_gpu_arm(args):
     if world > 1:
         extra["dp_check"] = dp_check(job, dev, world)
         failed = not extra["dp_check"]["ok"]
+        extra["exchange_timeline_per_rank"] = exchange_timeline(job, dev, world)
         # what the exchange leaves exposed: the same step without exchange and update
         ms_compute = job.timed(5, 1, barrier, update=False)
         (ms_compute,) = max_over_ranks([ms_compute], dev, world)

@@ -88,6 +88,9 @@ def main():
     ap.add_argument("--rotate", type=int, default=1,
                     help="number of weight matrices to rotate through (> 1: the weights of a call are not in L2, "
                          "as inside a network whose layers have different weights)")
+    ap.add_argument("--beside-wait-ms", type=float, default=0.0,
+                    help="run every timed call beside a barrier kernel on another stream that waits this long for a "
+                         "flag nothing sets (what a waiting kernel costs the kernels beside it)")
     a = ap.parse_args()
     if a.op == "probe":
         return probe()
@@ -159,13 +162,36 @@ def main():
     for _ in range(a.warmup):
         run()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.iters):
-        run()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / a.iters
+    if a.beside_wait_ms > 0:
+        # two "ranks" whose flag arrays live on this GPU; rank 1 never signals, so the barrier kernel
+        # waits until its time limit, records that in `status` and returns
+        lib = _lib.load()
+        side = torch.cuda.Stream()
+        flags = [torch.zeros(4, dtype=torch.int32, device=dev) for _ in range(2)]
+        ptrs = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+        status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        total = 0.0
+        for it in range(a.iters):
+            ready = torch.cuda.Event()
+            ready.record()
+            side.wait_event(ready)
+            _lib.check(lib.snb_peer_barrier(ptrs, 0, 2, it + 1, int(a.beside_wait_ms * 1e6), status.data_ptr(),
+                                            side.cuda_stream), "peer_barrier")
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        ms = total / a.iters
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.iters
     elems = a.B * ci_n * co_n
     msg = "%s B=%d CI=%d CO=%d: %.4f ms" % (a.op, a.B, ci_n, co_n, ms)
     if a.op in OPS_PER_ELEMENT:
