@@ -153,7 +153,7 @@ __global__ void check_index_kernel(const int* __restrict__ idx, long long n, int
 using namespace snb;
 
 // index [lists, count] int32 (the [S, G, count] lists of one operand flattened): checks that every
-// entry lies in [0, channels) and whether every list is strictly ascending.  Copies the verdict
+// entry lies in [0, channels) and whether every list is strictly ascending.  Copies the result
 // back and synchronises `stream`, so it is meant for debugging, not for the training loop.
 // *flags (host, optional) receives bit 0 = out of range, bit 1 = not ascending.
 extern "C" int snb_check_index_lists(const int* index, int lists, int count, int channels, int* flags, void* stream) {
