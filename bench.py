@@ -53,6 +53,10 @@ CONFIGS = {
 }
 HEADLINE = CONFIGS[1]
 ADAM = dict(lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=0.0)
+# limit of a GPU-side wait for a peer: generous, because the ranks reach their first step (module
+# loading, first-launch set-up) seconds apart on a busy host; a rank that is really gone still ends
+# the run with an error instead of a hang
+PEER_WAIT_S = 30.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (bound_fwd_kernel_64x256_512x5120x5120.md; inf_fwd_sk_kernel_masked_512x4619x4596.md,
@@ -216,9 +220,9 @@ class Job:
         torch.manual_seed(1 + rank)  # masks and data differ per rank, like the reference's seed + rank
         self.exchange = exchange
         if exchange == "copies":
-            self.opt = FlatAdamW(self.model, peer_memory=True, overlap=True, **ADAM)
+            self.opt = FlatAdamW(self.model, peer_memory=True, overlap=True, barrier_timeout_s=PEER_WAIT_S, **ADAM)
         elif exchange == "fused":
-            self.opt = FlatAdamW(self.model, peer_memory=True, overlap=False, **ADAM)
+            self.opt = FlatAdamW(self.model, peer_memory=True, overlap=False, barrier_timeout_s=PEER_WAIT_S, **ADAM)
         else:                                   # "nccl": one flat all-reduce; "none": local optimiser
             self.opt = FlatAdamW(self.model, peer_memory=False, **ADAM)
         pool = 4
