@@ -65,37 +65,6 @@ __device__ __forceinline__ float pow_pos(float a, float e) {
 // divides that by e.
 __device__ __forceinline__ float pow_pos_sum(float a, float e) { return ex2_approx(e * lg2_approx(a)); }
 
-// 2^(l * e) for l * e in [-120, ~0] without the special-function unit: the product is split into
-// its nearest integer n (read from the low mantissa bits of l * e + 1.5 * 2^23) and a remainder f
-// in [-0.5, 0.5], 2^f comes from a polynomial (DEG 4: 2.7e-6 relative, DEG 5: 2e-7), and n is added
-// to the exponent field.  The caller clamps l from below (l * e >= -120); a product above 0 by more
-// than rounding does not occur here because every ratio raised to a power is <= 1.
-// Two transcendentals per term at 16 per clock per SM bound the general-p kernels; moving part of
-// the exp2 work to the FMA pipe, which idles meanwhile, lifts that bound.
-template <int DEG>
-__device__ __forceinline__ float ex2_fma(float l, float e) {
-    constexpr float MAGIC = 12582912.0f;   // 1.5 * 2^23
-    const float zr = fmaf(l, e, MAGIC);
-    const float fl = zr - MAGIC;
-    const float f = fmaf(l, e, -fl);
-    float q;
-    if (DEG == 4) {
-        q = fmaf(f, 0.009570101276040077f, 0.05591785907745361f);
-        q = fmaf(q, f, 0.240247443318367f);
-        q = fmaf(q, f, 0.6931217908859253f);
-        q = fmaf(q, f, 0.9999992847442627f);
-    } else {
-        q = fmaf(f, 0.001327647129073739f, 0.009675540961325169f);
-        q = fmaf(q, f, 0.05550713092088699f);
-        q = fmaf(q, f, 0.24022120237350464f);
-        q = fmaf(q, f, 0.6931469440460205f);
-        q = fmaf(q, f, 1.0000001192092896f);
-    }
-    return __int_as_float(__float_as_int(q) + (__float_as_int(zr) << 23));
-}
-// which of the 16 terms of a batch take the FMA-pipe exp2: `n` of them, spread evenly
-__host__ __device__ constexpr bool poly_term(int e, int n) { return (e + 1) * n / 16 != e * n / 16; }
-
 // |r|^IP for integer IP (multiply chain) or |r|^e for IP < 0; forward terms.
 template <int IP>
 __device__ __forceinline__ float pow_abs(float r, float e) {
@@ -144,7 +113,7 @@ enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
 // StreamK), so all SMs stay busy whatever the shape and the mask sizes.  With `direct` the grid
 // has one CTA per tile and each CTA turns its sums into distances itself; otherwise every range
 // adds its partial sums into the zero-filled y with atomics and lp_finish_kernel takes the root.
-template <int WN, int MODE, int IP, bool NORMALISED, int POLY>
+template <int WN, int MODE, int IP, bool NORMALISED>
 __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
     constexpr int BM = 32, BN = 64 * WN, NT = WN * 32;
     extern __shared__ __align__(16) float smem[];
@@ -158,7 +127,6 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
     // worth testing only when most elements qualify: at p >= 48 the cut is |t|/M < 0.56
     const bool use_skip = NORMALISED && p.p >= 48.0f;
     const float skip_below = exp2f(-40.0f / p.p);
-    const float lg_floor = -120.0f / p.p;      // ex2_fma's range; (|t|/M)^p < 2^-120 is zero to the sum
 
   while (u < u_end) {
     const int tile = (int)(u / nk), kt_begin = (int)(u % nk);
@@ -242,10 +210,8 @@ __global__ void __launch_bounds__(WN * 32) lp_fwd_kernel(const LpFwdParams p) {
                     if (use_skip && __all_sync(0xffffffffu, big < skip_below)) continue;
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
-                        if (poly_term(2 * j, POLY)) acc[i][j] += ex2_fma<4>(fmaxf(lg2_approx(a0[j]), lg_floor), p.p);
-                        else acc[i][j] += pow_abs<IP>(a0[j], p.p);
-                        if (poly_term(2 * j + 1, POLY)) acc[i][j] += ex2_fma<4>(fmaxf(lg2_approx(a1[j]), lg_floor), p.p);
-                        else acc[i][j] += pow_abs<IP>(a1[j], p.p);
+                        acc[i][j] += pow_abs<IP>(a0[j], p.p);
+                        acc[i][j] += pow_abs<IP>(a1[j], p.p);
                     }
                 } else {
 #pragma unroll
@@ -321,7 +287,7 @@ constexpr int LPB_GLD = 36;
 // negligible and the hardware log2's absolute error of 2^-22, multiplied by p - 1, stays under
 // 7e-6 of a term; without the votes nothing separates the batches and the compiler overlaps
 // their log2 / exp2 chains.
-template <int IP, int NT, bool FINE, int POLY>
+template <int IP, int NT, bool FINE>
 __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdParams p) {
     constexpr int LPB_WLD = NT + 4;  // floats per W-tile row (+4: keeps 16-byte alignment, shifts banks)
     extern __shared__ __align__(16) float smem[];
@@ -338,7 +304,6 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
     // |u|^(p-1) < 2^-40 for a whole warp: the terms are dropped (the largest terms are ~1)
     const bool use_skip = p.pm1 >= 48.0f;
     const float skip_below = IP < 0 ? exp2f(-40.0f / fmaxf(p.pm1, 1e-3f)) : 0.f;
-    const float lg_floor = -120.0f / fmaxf(p.pm1, 1e-3f);   // ex2_fma's range; a term below 2^-120 is zero
 
   while (u < u_end) {
     const int unit = (int)(u / ntiles), t_begin = (int)(u % ntiles);
@@ -488,9 +453,7 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
                         const float gv = gp[4 * h + ii];
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            const float pw = poly_term(4 * ii + k, POLY) ? ex2_fma<5>(fmaxf(lg[ii][k], lg_floor), p.pm1)
-                                                                          : ex2_approx(p.pm1 * lg[ii][k]);
-                            const float ps = copysignf(pw, u[ii][k]);
+                            const float ps = copysignf(ex2_approx(p.pm1 * lg[ii][k]), u[ii][k]);
                             gx[4 * h + ii][k] = fmaf(gv, ps, gx[4 * h + ii][k]);
                             gwp[k] = fmaf(gv, ps, gwp[k]);
                         }
@@ -532,7 +495,7 @@ __global__ void __launch_bounds__(NT, IP < 0 ? 4 : 3) lp_bwd_kernel(const LpBwdP
 
 // One CTA per resident slot (SMs x CTAs per SM by the occupancy calculator), each with an equal
 // share of the work units; grad_x is zero-filled first because partial ranges add into it.
-template <int IP, bool FINE = true, int POLY = 0>
+template <int IP, bool FINE = true>
 static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
     constexpr int NT = 128;
     constexpr int SMEM = (2 * LPB_JT * (NT + 4) + 2 * 2 * LPB_JT * LPB_GLD) * (int)sizeof(float);
@@ -541,7 +504,7 @@ static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
     cudaGetDevice(&dev);
     std::atomic<int>& slot = cached[dev & 63];
     int cps = slot.load(std::memory_order_acquire);
-    auto kern = lp_bwd_kernel<IP, NT, FINE, POLY>;
+    auto kern = lp_bwd_kernel<IP, NT, FINE>;
     if (cps == 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         int occ = 0;
@@ -560,11 +523,11 @@ static cudaError_t launch_lp_bwd(const LpBwdParams& q, cudaStream_t st) {
 
 // p.m == nullptr with NORM: the maxima are in y and no scratch is available -> one CTA per tile,
 // finished in the kernel.  Otherwise equal (tile, k-tile) ranges over all resident CTA slots.
-template <int WN, int MODE, int IP, bool NORM, int POLY = 0>
+template <int WN, int MODE, int IP, bool NORM>
 static cudaError_t launch_lp_fwd(LpFwdParams p, cudaStream_t st) {
     constexpr int BN = 64 * WN;
     constexpr int SMEM = 2 * (32 + BN) * LDS * (int)sizeof(float);
-    auto kern = lp_fwd_kernel<WN, MODE, IP, NORM, POLY>;
+    auto kern = lp_fwd_kernel<WN, MODE, IP, NORM>;
     static std::atomic<int> cached[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -597,15 +560,11 @@ static cudaError_t launch_lp_fwd(LpFwdParams p, cudaStream_t st) {
     return cudaGetLastError();
 }
 
-template <int IP, bool NORM, int POLY = 0>
+template <int IP, bool NORM>
 static cudaError_t dispatch_lp_mode(const LpFwdParams& p, cudaStream_t st) {
-    if (p.ci || p.co) return launch_lp_fwd<4, MODE_GATHER, IP, NORM, POLY>(p, st);
+    if (p.ci || p.co) return launch_lp_fwd<4, MODE_GATHER, IP, NORM>(p, st);
     const bool vec = (p.CI % 4 == 0) && (p.W_CI % 4 == 0) && aligned16(p.x) && aligned16(p.w);
-    return vec ? launch_lp_fwd<4, MODE_VEC, IP, NORM, POLY>(p, st) : launch_lp_fwd<4, MODE_SCALAR, IP, NORM, POLY>(p, st);
-}
-static int tune_poly(const char* name) {   // TEMPORARY tuning switch
-    const char* v = getenv(name);
-    return v ? atoi(v) : -1;
+    return vec ? launch_lp_fwd<4, MODE_VEC, IP, NORM>(p, st) : launch_lp_fwd<4, MODE_SCALAR, IP, NORM>(p, st);
 }
 
 static int integer_power(float p) {
@@ -636,13 +595,7 @@ static int lp_forward_impl(const float* x, const float* w, int B, int CO, int CI
         float* maxima = scratch ? scratch : y;
         SNB_CUDA(inf_forward_values(x, w, maxima, w_index_ci, w_index_co, B, CO, CI, W_CI, st));
         q.m = scratch;
-        switch (tune_poly("SNB_LP_POLY_F")) {
-            case 0: SNB_CUDA((dispatch_lp_mode<-1, true, 0>(q, st))); break;
-            case 6: SNB_CUDA((dispatch_lp_mode<-1, true, 6>(q, st))); break;
-            case 10: SNB_CUDA((dispatch_lp_mode<-1, true, 10>(q, st))); break;
-            case 12: SNB_CUDA((dispatch_lp_mode<-1, true, 12>(q, st))); break;
-            default: SNB_CUDA((dispatch_lp_mode<-1, true, 8>(q, st))); break;
-        }
+        SNB_CUDA(dispatch_lp_mode<-1, true>(q, st));
         return SNB_OK;
     }
     switch (integer_power(p)) {
@@ -706,21 +659,8 @@ static int lp_backward(const float* g, const float* x, const float* w, const flo
         case 6: SNB_CUDA(launch_lp_bwd<6>(q, st)); break;
         case 7: SNB_CUDA(launch_lp_bwd<7>(q, st)); break;
         default:
-            if (p - 1.0f >= 40.0f) {
-                switch (tune_poly("SNB_LP_POLY_B")) {
-                    case 0: SNB_CUDA((launch_lp_bwd<-1, true, 0>(q, st))); break;
-                    case 6: SNB_CUDA((launch_lp_bwd<-1, true, 6>(q, st))); break;
-                    case 8: SNB_CUDA((launch_lp_bwd<-1, true, 8>(q, st))); break;
-                    default: SNB_CUDA((launch_lp_bwd<-1, true, 4>(q, st))); break;
-                }
-            } else {
-                switch (tune_poly("SNB_LP_POLY_B")) {
-                    case 0: SNB_CUDA((launch_lp_bwd<-1, false, 0>(q, st))); break;
-                    case 6: SNB_CUDA((launch_lp_bwd<-1, false, 6>(q, st))); break;
-                    case 8: SNB_CUDA((launch_lp_bwd<-1, false, 8>(q, st))); break;
-                    default: SNB_CUDA((launch_lp_bwd<-1, false, 4>(q, st))); break;
-                }
-            }
+            if (p - 1.0f >= 40.0f) SNB_CUDA((launch_lp_bwd<-1, true>(q, st)));
+            else SNB_CUDA((launch_lp_bwd<-1, false>(q, st)));
             break;
     }
     SNB_CUDA(cudaGetLastError());
