@@ -87,6 +87,21 @@ int snb_inf_dist_forward_ws(const float* x, const float* w, int B, int CO, int C
                             float* y, int* pos, const int* w_index_ci, const int* w_index_co,
                             int W_CO, int W_CI, void* workspace, size_t workspace_bytes, void* stream);
 
+/* snb_inf_dist_forward_ws for index lists in ascending order (every list strictly increasing), the
+ * order in which the sampler (snb_sample_mask) and the reference's sample_mask
+ * (core/models/norm_dist.py:14-17, which ends with torch.sort) produce them.  With a 16-byte aligned
+ * workspace of snb_inf_dist_forward_sorted_workspace_bytes(B, CO, W_CI) bytes (merge keys, a
+ * [B, W_CI] copy of x with NaN in the dropped columns, inverse lists), W_CI a multiple of 4, a 16-byte
+ * aligned w and at least 3/4 of the columns kept, W is read along whole rows with 16-byte copies: a
+ * NaN difference never enters the maximum, and full-column order is list order, so y and pos are
+ * bit-identical to snb_inf_dist_forward.  Otherwise it forwards to snb_inf_dist_forward_ws.  Lists
+ * in another order still give exact y, but ties for the maximum may then resolve to another of the
+ * tied positions.  No counterpart in the reference. */
+size_t snb_inf_dist_forward_sorted_workspace_bytes(int B, int CO, int W_CI);
+int snb_inf_dist_forward_sorted_ws(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                                   float* y, int* pos, const int* w_index_ci, const int* w_index_co,
+                                   int W_CO, int W_CI, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Unmasked snb_inf_dist_forward for callers that must not allocate device memory.  It has no
  * counterpart in the reference.  Who needs it: a host that binds this C ABI directly — a C or C++
  * serving loop, a plugin inside another runtime — has no tensor library to hand it cached scratch,
@@ -261,8 +276,9 @@ int snb_trim_scratch(void);
 /* ---- whole layers and the model head (G = 1, HW = 1) ---------------------------------------- */
 
 /* One fully connected norm-distance layer of the training / plain forward in one call: the distance
- * (p = inf: snb_inf_dist_forward_ws when pos is given, snb_inf_dist_forward_nograd when pos is NULL
- * and there are no index lists; finite p: snb_norm_dist_forward_ws) into y_dist, then, when `mean`
+ * (p = inf: snb_inf_dist_forward_sorted_ws when pos is given - index lists must be ascending -,
+ * snb_inf_dist_forward_nograd when pos is NULL and there are no index lists; finite p:
+ * snb_norm_dist_forward_ws) into y_dist, then, when `mean`
  * is not NULL, the batch mean per channel into mean [W_CO] with the momentum update of running_mean
  * (may be NULL), and out[b, j] = (y_dist[b, j] - mean[c]) + bias[c] with c = w_index_co[s_b][j] (mean
  * and bias optional; out may be y_dist).  workspace as in the _ws entry points (may be NULL).

@@ -3,7 +3,7 @@
     python run_case.py --op bound_nograd --B 512 --CI 5120 --CO 5120 --iters 5
 
 Used for quick timing of a single kernel and as the small, self-terminating command that
-profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_nograd,
+profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_fwd_sorted (its ascending-list form), inf_nograd,
 inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_shift, sort_nograd,
 sort_bound, sort_fwd (values + positions), sort_bwd (K = 10, q = 0.9), probe (hardware probes).
 """
@@ -19,7 +19,7 @@ from sortnet_b200 import _lib                      # noqa: E402
 from sortnet_b200 import norm_dist_cuda as C       # noqa: E402
 from sortnet_b200.layers import sample_mask        # noqa: E402
 
-OPS_PER_ELEMENT = {"inf_fwd": 2, "inf_nograd": 2, "bound_nograd": 6, "bound_fwd": 6, "lp_fwd": 4, "lp_bwd": 6, "lp_bwd_x": 6}
+OPS_PER_ELEMENT = {"inf_fwd": 2, "inf_fwd_sorted": 2, "inf_nograd": 2, "bound_nograd": 6, "bound_fwd": 6, "lp_fwd": 4, "lp_bwd": 6, "lp_bwd_x": 6}
 
 
 PROBES = ["packed sub + max3abs", "2 scalar sub + 2 max", "2 scalar sub + max3abs", "packed sub + 2 max",
@@ -83,6 +83,8 @@ def main():
     ap.add_argument("--CO", type=int, default=5120)
     ap.add_argument("--keep", type=float, default=1.0)
     ap.add_argument("--p", type=float, default=8.0)
+    ap.add_argument("--mask", choices=("both", "ci", "co"), default="both",
+                    help="with --keep < 1: which index lists to draw (co = kept rows of W only, like a first layer)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--rotate", type=int, default=1,
@@ -99,8 +101,8 @@ def main():
     S = (a.B + 31) // 32
     ci = co = None
     if a.keep < 1.0:
-        ci = sample_mask(S, 1, a.CI, a.keep, dev)
-        co = sample_mask(S, 1, a.CO, a.keep, dev)
+        ci = sample_mask(S, 1, a.CI, a.keep, dev) if a.mask in ("both", "ci") else None
+        co = sample_mask(S, 1, a.CO, a.keep, dev) if a.mask in ("both", "co") else None
     ci_n = a.CI if ci is None else ci.size(-1)
     co_n = a.CO if co is None else co.size(-1)
     ws = [torch.randn(a.CO, a.CI, device=dev) for _ in range(max(a.rotate, 1))]
@@ -131,6 +133,8 @@ def main():
         calls[0] += 1
         if a.op == "inf_fwd":
             C.inf_dist_forward(x, w, y, pos, 1, ci, co)
+        elif a.op == "inf_fwd_sorted":
+            C.inf_dist_forward_sorted(x, w, y, pos, ci, co)
         elif a.op == "inf_nograd":
             C.inf_dist_forward_nograd(x, w, y, 1)
         elif a.op == "inf_bwd":

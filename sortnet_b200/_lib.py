@@ -16,6 +16,7 @@ _F = ctypes.c_float
 SIGNATURES = {
     "snb_inf_dist_forward": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P],
     "snb_inf_dist_forward_ws": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, ctypes.c_size_t, _P],
+    "snb_inf_dist_forward_sorted_ws": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, ctypes.c_size_t, _P],
     "snb_inf_dist_forward_noalloc": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "snb_inf_dist_forward_nograd": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
     "snb_inf_dist_backward_input": [_P, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -89,6 +90,8 @@ def load(build_if_missing: bool = False):
     lib.snb_inf_dist_forward_noalloc_max_outputs.restype = ctypes.c_int
     lib.snb_inf_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.snb_inf_dist_forward_workspace_bytes.restype = ctypes.c_size_t
+    lib.snb_inf_dist_forward_sorted_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    lib.snb_inf_dist_forward_sorted_workspace_bytes.restype = ctypes.c_size_t
     lib.snb_norm_dist_forward_workspace_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_float]
     lib.snb_norm_dist_forward_workspace_bytes.restype = ctypes.c_size_t
     _lib = lib

@@ -28,11 +28,12 @@ struct InfFwdParams {
     const int* co;  // [S][CO] kept rows of W per sub-batch, or null
     int B, CO, CI;  // compact sizes seen by x / y
     int W_CI;       // leading dimension of w
+    const int* inv; // [S][CI] full column -> compact position (full-width form, see expand_rows_kernel) or null
 };
 
 constexpr int CHUNK_TILES = 1;  // argmax chunk = one k-tile = 32 reduction steps
 
-enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2 };
+enum { MODE_VEC = 0, MODE_SCALAR = 1, MODE_GATHER = 2, MODE_ROWVEC = 3 };
 
 // Four reduction steps of one output: acc = max(acc, |x_k - w_k|), k = 0..3, operands given as
 // two 64-bit register pairs each: packed subtracts + three-input |.|-max.  All instruction forms of
@@ -46,17 +47,82 @@ __device__ __forceinline__ void linf_step(float& acc, const ulonglong2& x, const
     acc = max3abs(acc, a, b);
 }
 
-// Turns the chunk id left in pos by the tracking kernel into the reference's argmax word.
+// Turns the chunk id left by the tracking kernel into the reference's argmax word.  Four lanes
+// share one output: each rescans eight consecutive elements of the output's 32-element chunk
+// (32 contiguous bytes of the x row and of the W row, two 16-byte loads each), keeps the
+// lowest element that equals y, and two shuffles pick the lowest of the four.  Every lane reads its
+// output's (chunk, y, row) itself - the four loads of a group coalesce into one - so nothing is
+// broadcast by shuffles and a thread's sixteen operand loads are all independent.
+// FROM_WS: the tracking kernel ran split over k and left (value bits << 32 | ~chunk) keys in the
+// 64-bit workspace instead of y / pos; y is written here too.
+// Needs dense columns (no ci list), CI and W_CI multiples of 4 and 16-byte aligned x and w.
+template <bool FROM_WS>
+__global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, const unsigned long long* __restrict__ keys) {
+    static_assert(CHUNK_TILES * BK == 32, "four lanes x eight elements per chunk");
+    const int q4 = threadIdx.x & 3;
+    const int m = blockIdx.x, n = blockIdx.y * 64 + (threadIdx.x >> 2);   // grid: B x ceil(CO / 64)
+    const bool have = n < p.CO;
+    const size_t o = have ? (size_t)m * p.CO + n : 0;
+    const int s = m / SNB_SUB_BATCH;
+    int chunk = -1;
+    float yv = 0.f;
+    if (have) {
+        if (FROM_WS) {
+            const unsigned long long key = keys[o];
+            yv = __uint_as_float((uint32_t)(key >> 32));
+            chunk = (int)(0xffffffffu - (uint32_t)key);      // 0xffffffff - 0 = -1: no chunk
+        } else {
+            chunk = p.pos[o];
+            yv = p.y[o];
+        }
+    }
+    constexpr uint32_t NONE = 0xffffu;
+    uint32_t mine = NONE;                                    // (element of the chunk << 1) | (x - w < 0)
+    if (chunk >= 0) {
+        const int row = p.co ? p.co[(size_t)s * p.CO + n] : n;
+        const int c0 = chunk * 32 + q4 * 8;
+        const float* xr = p.x + (size_t)m * p.CI;
+        const float* wr = p.w + (size_t)row * p.W_CI;
+        float xv[8], wv[8];
+        bool ok[8];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const bool in = c0 + 4 * h < p.CI;               // CI % 4 == 0: a quad is inside or outside
+            const float4 a = in ? *reinterpret_cast<const float4*>(xr + c0 + 4 * h) : make_float4(0, 0, 0, 0);
+            const float4 b = in ? *reinterpret_cast<const float4*>(wr + c0 + 4 * h) : make_float4(0, 0, 0, 0);
+            xv[4 * h] = a.x; xv[4 * h + 1] = a.y; xv[4 * h + 2] = a.z; xv[4 * h + 3] = a.w;
+            wv[4 * h] = b.x; wv[4 * h + 1] = b.y; wv[4 * h + 2] = b.z; wv[4 * h + 3] = b.w;
+            ok[4 * h] = ok[4 * h + 1] = ok[4 * h + 2] = ok[4 * h + 3] = in;
+        }
+#pragma unroll
+        for (int e = 7; e >= 0; e--) {                       // descending: the lowest match stays
+            const float t = xv[e] - wv[e];
+            if (ok[e] && fabsf(t) == yv) mine = (uint32_t)((q4 * 8 + e) << 1) | (t < 0.f ? 1u : 0u);
+        }
+    }
+    mine = min(mine, __shfl_xor_sync(0xffffffffu, mine, 1));
+    mine = min(mine, __shfl_xor_sync(0xffffffffu, mine, 2));
+    if (!have || q4 != 0) return;
+    uint32_t word = 0;
+    if (mine != NONE) {
+        int idx = chunk * 32 + (int)(mine >> 1);
+        if (p.inv) idx = p.inv[(size_t)s * p.CI + idx];      // full-width column -> position in the kept list
+        word = (uint32_t)idx | ((mine & 1u) ? SNB_SIGN_BIT : 0u);
+    }
+    if (FROM_WS) p.y[o] = yv;
+    p.pos[o] = (int)word;
+}
+
+// The same for operands that cannot be read with aligned 16-byte loads (a kept-column list, odd
+// row lengths):
 // One warp owns 32 consecutive outputs of one row; for each of them the 32 lanes load the 32
 // elements of its chunk (coalesced in x, one row segment of W), compare with y and the lowest
 // matching lane gives the index.  RESOLVE_BATCH outputs are in flight per warp to overlap the
 // index -> weight load chains (the kernel is bound by their latency).
-// FROM_WS: the tracking kernel ran split over k and left (value bits << 32 | ~chunk) keys in the
-// 64-bit workspace instead of y / pos; y is written here too.
 constexpr int RESOLVE_BATCH = 8;
 
 template <bool FROM_WS>
-__global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, const unsigned long long* __restrict__ keys) {
+__global__ void __launch_bounds__(256) inf_resolve_lists_kernel(const InfFwdParams p, const unsigned long long* __restrict__ keys) {
     static_assert(CHUNK_TILES * BK == 32, "one lane per chunk element");
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * 32;
@@ -114,6 +180,21 @@ __global__ void __launch_bounds__(256) inf_resolve_kernel(const InfFwdParams p, 
     if (have) p.pos[o] = (int)my_word;
 }
 
+static cudaError_t launch_resolve(const InfFwdParams& p, const unsigned long long* keys, bool from_ws, cudaStream_t st) {
+    const dim3 grid(p.B, (p.CO + 63) / 64);
+    const bool vec = !p.ci && (p.CI % 4 == 0) && (p.W_CI % 4 == 0) && aligned16(p.x) && aligned16(p.w) &&
+                     (p.CO + 63) / 64 <= 65535;
+    const dim3 lists_grid((p.CO + 31) / 32, (p.B + 7) / 8);
+    if (from_ws) {
+        if (vec) inf_resolve_kernel<true><<<grid, 256, 0, st>>>(p, keys);
+        else inf_resolve_lists_kernel<true><<<lists_grid, 256, 0, st>>>(p, keys);
+    } else {
+        if (vec) inf_resolve_kernel<false><<<grid, 256, 0, st>>>(p, nullptr);
+        else inf_resolve_lists_kernel<false><<<lists_grid, 256, 0, st>>>(p, nullptr);
+    }
+    return cudaGetLastError();
+}
+
 // Sparse backward: one CTA per batch row.  grad_x of the row is accumulated in shared
 // memory (many outputs of a row share an argmax column) and written once, so grad_x needs
 // neither a memset nor global atomics; grad_w gets one global reduction per output.
@@ -167,6 +248,36 @@ __global__ void __launch_bounds__(256) inf_bwd_wide_kernel(const float* __restri
     }
 }
 
+// Full-width form of a column-masked input: xw[b][k] = x[b][c] where k = ci[s][c], NaN in every
+// dropped column, and inv[s][k] = c (or -1).  max.f32 returns the other operand when one is NaN, so a
+// NaN difference never reaches the accumulator and the distance over all W_CI columns of xw equals
+// the distance over the kept columns, bit for bit; in exchange W is read along whole rows with
+// 16-byte copies instead of one 4-byte copy per kept element.  With ascending lists (the
+// sampler's and the reference's, core/models/norm_dist.py:14-17) full-column order is compact order,
+// so "first chunk that reached the maximum, first equal element in it" picks the same position.
+// One CTA per batch row; the first row of every sub-batch also writes the inverse list.
+__global__ void __launch_bounds__(256) expand_rows_kernel(const float* __restrict__ x, const int* __restrict__ ci, int B,
+                                                          int CI, int W_CI, float* __restrict__ xw,
+                                                          int* __restrict__ inv) {
+    const int b = blockIdx.x, s = b / SNB_SUB_BATCH;
+    const bool first = (b % SNB_SUB_BATCH) == 0;
+    float* row = xw + (size_t)b * W_CI;
+    int* inv_s = inv + (size_t)s * W_CI;
+    const float nan = __int_as_float(0x7fc00000);
+    for (int k = threadIdx.x; k < W_CI; k += blockDim.x) {
+        row[k] = nan;
+        if (first) inv_s[k] = -1;
+    }
+    __syncthreads();   // this CTA's own global writes are ordered for its threads
+    const int* ci_s = ci + (size_t)s * CI;
+    const float* xr = x + (size_t)b * CI;
+    for (int c = threadIdx.x; c < CI; c += blockDim.x) {
+        const int k = ci_s[c];
+        row[k] = xr[c];
+        if (first) inv_s[k] = c;
+    }
+}
+
 // Forward kernel (dense or index-masked operands, with or without argmax tracking), stream-K over
 // (tile, k-tile) pairs: every CTA of a persistent grid does the same number of k-tiles, so the
 // run time does not depend on how the tile count divides the SMs (with 32-row masked tiles and
@@ -193,7 +304,7 @@ __device__ __forceinline__ unsigned long long pack_key(float v, uint32_t chunk16
 template <int WM, int WN, int MODE, bool TRACK>
 __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkParams p) {
     constexpr int BM = 32 * WM, BN = 64 * WN, NT = WM * WN * 32;
-    static_assert(MODE != MODE_GATHER || WM == 1, "masked tiles are one 32-row sub-batch");
+    static_assert((MODE != MODE_GATHER && MODE != MODE_ROWVEC) || WM == 1, "masked tiles are one 32-row sub-batch");
     extern __shared__ __align__(16) float smem[];
     float* xs = smem;
     float* ws = smem + 2 * BM * LDS;
@@ -208,6 +319,7 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
         const int kb = (int)min((long long)sk.nk, ka + (u1 - u0));
         const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
         GatherW<BN, NT> gw;
+        RowVecW<BN, NT> rw;
         const int* ci_s = nullptr;
         if (MODE == MODE_GATHER) {
             const int s = m0 / SNB_SUB_BATCH;
@@ -215,10 +327,17 @@ __global__ void __launch_bounds__(WM* WN * 32) inf_fwd_sk_kernel(const InfSkPara
             gw.init_rows(p.co ? p.co + (size_t)s * p.CO : nullptr, n0, p.CO, p.W_CI, tid);
             gw.fetch_cols(ci_s, ka * BK, p.CI, tid);
         }
+        if (MODE == MODE_ROWVEC)
+            rw.init_rows(p.co ? p.co + (size_t)(m0 / SNB_SUB_BATCH) * p.CO : nullptr, n0, p.CO, p.W_CI, tid);
         auto stage = [&](int kt, int st) {
             float* xd = xs + st * BM * LDS;
             float* wd = ws + st * BN * LDS;
-            if (MODE == MODE_VEC) {
+            if (MODE == MODE_ROWVEC) {
+                // full-width form: x holds all W_CI columns (NaN where a column was dropped, which
+                // the three-input max ignores), W rows come through the kept-row list
+                stage_dense_vec<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
+                rw.stage(wd, p.w, kt * BK, p.CI, tid);
+            } else if (MODE == MODE_VEC) {
                 stage_dense_vec<BM, NT>(xd, p.x, m0, p.B, p.CI, kt * BK, p.CI, tid);
                 stage_dense_vec<BN, NT>(wd, p.w, n0, p.CO, p.W_CI, kt * BK, p.CI, tid);
             } else if (MODE == MODE_SCALAR) {
@@ -366,9 +485,11 @@ static cudaError_t launch_sk(InfSkParams p, bool* split, cudaStream_t st) {
 // *split tells whether tiles were shared between CTAs; for TRACK that means the result is in
 // `keys` (workspace) and still has to be turned into y / pos by the resolve kernel.
 template <bool TRACK>
-static cudaError_t dispatch_fwd(const InfFwdParams& q, unsigned long long* keys, bool* split, cudaStream_t st) {
+static cudaError_t dispatch_fwd(const InfFwdParams& q, unsigned long long* keys, bool* split, cudaStream_t st,
+                                bool full_width = false) {
     InfSkParams p{q.x, q.w, q.y, q.pos, keys, q.ci, q.co, q.B, q.CO, q.CI, q.W_CI, 0, 0};
     const int sms = sm_count();
+    if (full_width) return launch_sk<1, 4, MODE_ROWVEC, TRACK>(p, split, st);
     if (q.ci || q.co) {
         const long wide = (long)((q.B + 31) / 32) * ((q.CO + 255) / 256);
         return wide >= sms / 2 ? launch_sk<1, 4, MODE_GATHER, TRACK>(p, split, st)
@@ -419,10 +540,7 @@ static int inf_forward_impl(const float* x, const float* w, int B, int CO, int C
     InfFwdParams p{x, w, y, pos, ci, co, B, CO, CI, W_CI};
     bool split = false;
     SNB_CUDA(dispatch_fwd<true>(p, keys, &split, st));
-    dim3 grid((CO + 31) / 32, (B + 7) / 8);
-    if (split) inf_resolve_kernel<true><<<grid, 256, 0, st>>>(p, keys);
-    else inf_resolve_kernel<false><<<grid, 256, 0, st>>>(p, nullptr);
-    SNB_CUDA(cudaGetLastError());
+    SNB_CUDA(launch_resolve(p, keys, split, st));
     return SNB_OK;
 }
 
@@ -448,6 +566,61 @@ extern "C" int snb_inf_dist_forward_ws(const float* x, const float* w, int B, in
     }
     return inf_forward_impl(x, w, B, CO, CI, G, HW, y, pos, w_index_ci, w_index_co, W_CO, W_CI, keys,
                             (cudaStream_t)stream);
+}
+
+// Workspace of the ascending-list form: merge keys [B * CO] u64, then the full-width input
+// [B * W_CI] f32 (16-byte aligned), then the inverse lists [S * W_CI] i32.
+static size_t sorted_ws_input_offset(int B, int CO) {
+    return (sizeof(unsigned long long) * (size_t)B * (size_t)CO + 15) & ~(size_t)15;
+}
+extern "C" size_t snb_inf_dist_forward_sorted_workspace_bytes(int B, int CO, int W_CI) {
+    if (B <= 0 || CO <= 0 || W_CI <= 0) return 0;
+    const size_t S = (size_t)(B + SNB_SUB_BATCH - 1) / SNB_SUB_BATCH;
+    return sorted_ws_input_offset(B, CO) + sizeof(float) * (size_t)B * W_CI + sizeof(int) * S * W_CI;
+}
+
+// Masked forward whose index lists are in ascending order (every list strictly increasing), as
+// the sampler and the reference's sample_mask produce them.  Same results as
+// snb_inf_dist_forward_ws; with enough workspace and 16-byte aligned rows of W it runs in the
+// full-width form (expand_rows_kernel), otherwise through the general masked path.  Lists in
+// another order still give exact distances, but ties for the maximum between different columns
+// may then resolve to another of the tied positions than the reference's scan order would.
+extern "C" int snb_inf_dist_forward_sorted_ws(const float* x, const float* w, int B, int CO, int CI, int G, int HW,
+                                              float* y, int* pos, const int* w_index_ci, const int* w_index_co,
+                                              int W_CO, int W_CI, void* workspace, size_t workspace_bytes,
+                                              void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool masked = w_index_ci || w_index_co;
+    bool fast = masked && G == 1 && HW == 1 && workspace && pos && (W_CI % 4 == 0) && aligned16(w) &&
+                !(reinterpret_cast<uintptr_t>(workspace) & 15u) &&
+                workspace_bytes >= snb_inf_dist_forward_sorted_workspace_bytes(B, CO, W_CI) &&
+                (long long)B * W_CI < (1ll << 31);
+    // computing the dropped columns too must cost less than the vector copies save
+    if (fast && w_index_ci && (long long)CI * 4 < (long long)W_CI * 3) fast = false;
+    if (fast && !w_index_ci && !aligned16(x)) fast = false;
+    if (!fast)
+        return snb_inf_dist_forward_ws(x, w, B, CO, CI, G, HW, y, pos, w_index_ci, w_index_co, W_CO, W_CI, workspace,
+                                       workspace_bytes, stream);
+    int rc = check_fwd(x, w, y, B, CO, CI, G, HW, W_CO, W_CI, w_index_ci, w_index_co);
+    if (rc) return rc;
+    if ((W_CI + CHUNK_TILES * BK - 1) / (CHUNK_TILES * BK) >= 0xffff) return SNB_ERR_TOO_LARGE;
+    unsigned long long* keys = (unsigned long long*)workspace;
+    const float* xin = x;
+    const int* inv = nullptr;
+    if (w_index_ci) {
+        float* xw = reinterpret_cast<float*>(static_cast<char*>(workspace) + sorted_ws_input_offset(B, CO));
+        int* inv_w = reinterpret_cast<int*>(xw + (size_t)B * W_CI);
+        expand_rows_kernel<<<B, 256, 0, st>>>(x, w_index_ci, B, CI, W_CI, xw, inv_w);
+        SNB_CUDA(cudaGetLastError());
+        xin = xw;
+        inv = inv_w;
+    }
+    // the kernels see a dense input of W_CI columns and a row-masked W
+    InfFwdParams p{xin, w, y, pos, nullptr, w_index_co, B, CO, W_CI, W_CI, inv};
+    bool split = false;
+    SNB_CUDA(dispatch_fwd<true>(p, keys, &split, st, true));
+    SNB_CUDA(launch_resolve(p, keys, split, st));
+    return SNB_OK;
 }
 
 extern "C" int snb_inf_dist_forward_nograd(const float* x, const float* w, int B, int CO, int CI,

@@ -212,8 +212,8 @@ extern "C" int snb_layer_forward(const float* x, const float* w, int B, int CO, 
     if (rc) return rc;
     if (isinf(p)) {
         if (pos)
-            rc = snb_inf_dist_forward_ws(x, w, B, CO, CI, 1, 1, y_dist, pos, w_index_ci, w_index_co, W_CO, W_CI,
-                                         workspace, workspace_bytes, stream);
+            rc = snb_inf_dist_forward_sorted_ws(x, w, B, CO, CI, 1, 1, y_dist, pos, w_index_ci, w_index_co, W_CO, W_CI,
+                                                workspace, workspace_bytes, stream);
         else if (!w_index_ci && !w_index_co)
             rc = snb_inf_dist_forward_nograd(x, w, B, CO, CI, 1, 1, y_dist, stream);
         else

@@ -93,6 +93,32 @@ struct GatherW {
     }
 };
 
+// Rows of W picked through a per-sub-batch index list, all columns of each row: 16-byte copies
+// along the row like stage_dense_vec (requires W_CI % 4 == 0 and a 16-byte aligned base).  Every
+// thread keeps the element offsets of the ROWS / (NT / 8) rows it copies from in registers.
+template <int ROWS, int NT>
+struct RowVecW {
+    static constexpr int RPT = ROWS / (NT / 8);
+    int rowoff[RPT];  // element offset of the row start in W, or -1 past the last row
+
+    __device__ __forceinline__ void init_rows(const int* __restrict__ co_s, int n0, int CO, int W_CI, int tid) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const int n = n0 + (tid >> 3) + (NT / 8) * i;
+            rowoff[i] = n < CO ? (co_s ? co_s[n] : n) * W_CI : -1;
+        }
+    }
+    __device__ __forceinline__ void stage(float* s, const float* __restrict__ w, int k0, int K, int tid) const {
+        const int kc = (tid & 7) * 4;
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const bool ok = rowoff[i] >= 0 && k0 + kc < K;
+            const float* src = ok ? w + rowoff[i] + k0 + kc : w;
+            cp_async16(smem_u32(s + ((tid >> 3) + (NT / 8) * i) * LDS + kc), src, ok ? 16 : 0);
+        }
+    }
+};
+
 }  // namespace snb
 
 namespace snb {

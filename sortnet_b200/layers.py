@@ -233,7 +233,10 @@ class NormDist(nn.Module):
         return 1.0 if self.dropout is None else self.dropout
 
     def forward(self, x=None, lower=None, upper=None, mask_in=None, mask_out=None, sort_eval=False):
-        """With masks (training): x is compact over `mask_in`, the result compact over `mask_out`.
+        """With masks (training): x is compact over `mask_in`, the result compact over `mask_out`;
+        every index list must be ascending, as `sample_mask` returns it (the l-inf forward then reads
+        W along whole rows; lists in another order would still give exact distances, but ties for
+        the maximum could resolve to another tied position than the reference's).
         Without masks: the l-p / l-inf distance of the point value and, when a box
         (lower, upper) is given, its interval bounds (p must be inf).  `sort_eval=True` replaces
         the distance by the deterministic sort neuron with q = `dropout` (the expectation of
@@ -258,7 +261,7 @@ class NormDist(nn.Module):
                 return self._eval_linf(x, lower if box else None, upper if box else None)
         x3, l3, u3 = (None if z is None else z.unsqueeze(-1).contiguous() for z in (x, lower, upper))
         if masked:
-            x3 = ops.norm_dist_dropout(x3, self.weight, mask_in, mask_out, self.p)
+            x3 = ops.norm_dist_dropout_ascending(x3, self.weight, mask_in, mask_out, self.p)
         elif not sort_eval:
             if x3 is not None:
                 x3 = ops.norm_dist(x3, self.weight, self.p)

@@ -74,7 +74,7 @@ def _dims(x, out):
 
 # Kernels launched by each C entry point (memsets are not counted).
 _KERNELS = {
-    "snb_inf_dist_forward": 2, "snb_inf_dist_forward_ws": 2, "snb_inf_dist_forward_nograd": 1, "snb_inf_dist_backward_input": 1,
+    "snb_inf_dist_forward": 2, "snb_inf_dist_forward_ws": 2, "snb_inf_dist_forward_sorted_ws": 3, "snb_inf_dist_forward_nograd": 1, "snb_inf_dist_backward_input": 1,
     "snb_inf_dist_backward_input_weight": 1, "snb_norm_dist_forward": 1, "snb_norm_dist_forward_ws": 2, "snb_norm_dist_backward_input": 1,
     "snb_norm_dist_backward_input_weight": 1, "snb_bound_inf_dist_forward_nograd": 1,
     "snb_bound_inf_dist_forward": 1, "snb_bound_inf_dist_backward_input": 1,
@@ -154,6 +154,26 @@ def inf_dist_forward(input, weight, output, pos, G, w_index_ci=None, w_index_co=
     _call(dev, input, "snb_inf_dist_forward_ws", (B, CO, CI),
           _ptr(input), _ptr(weight), B, CO, CI, G, HW, _ptr(output), _ptr(pos), _ptr(w_index_ci),
           _ptr(w_index_co), weight.size(0), weight.size(1) * G, ws.data_ptr(), ws.numel() * 8)
+
+
+def inf_dist_forward_sorted(input, weight, output, pos, w_index_ci=None, w_index_co=None):
+    """inf_dist_forward (G = 1) for index lists in ascending order, as sample_mask and the reference's
+    sampler (core/models/norm_dist.py:14-17) produce them: same results, W read along whole rows
+    (snb_inf_dist_forward_sorted_ws).  No counterpart in the reference's extension."""
+    _check(input, "input"); _check(weight, "weight"); _check(output, "output")
+    _check(pos, "pos", torch.int32)
+    B, CO, CI, HW = _dims(input, output)
+    S = (B + _SUB_BATCH - 1) // _SUB_BATCH
+    _check_opt_index(w_index_ci, "w_index_ci", S, CI, 1, weight.size(1))
+    _check_opt_index(w_index_co, "w_index_co", S, CO, 1, weight.size(0))
+    if output.size(0) != B or pos.shape != output.shape:
+        raise RuntimeError("output / pos shape mismatch")
+    dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
+    nbytes = _lib.load().snb_inf_dist_forward_sorted_workspace_bytes(B, CO, weight.size(1))
+    ws = torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=dev)
+    _call(dev, input, "snb_inf_dist_forward_sorted_ws", (B, CO, CI),
+          _ptr(input), _ptr(weight), B, CO, CI, 1, HW, _ptr(output), _ptr(pos), _ptr(w_index_ci),
+          _ptr(w_index_co), weight.size(0), weight.size(1), ws.data_ptr(), ws.numel() * 8)
 
 
 def inf_dist_forward_nograd(input, weight, output, G):

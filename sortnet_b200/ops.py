@@ -21,6 +21,7 @@ import math
 
 import torch
 
+from . import _lib
 from . import norm_dist_cuda as _C
 
 INF = float("inf")
@@ -37,14 +38,17 @@ def _wants_grad(*tensors):
 
 # One implementation serves the plain and the masked distance operator: the plain one is the
 # masked one with both index lists absent.
-def _dist_forward(ctx, x, weight, ci, co, group, p, record):
+def _dist_forward(ctx, x, weight, ci, co, group, p, record, ascending=False):
     n_out = weight.size(0) if co is None else co.size(-1) * group
     y = torch.empty(x.size(0), n_out, x.size(2), device=x.device, dtype=torch.float32)
     ctx.group, ctx.p, ctx.masks = group, p, (ci, co)
     if math.isinf(p):
         if record:
             pos = torch.empty(y.shape, device=x.device, dtype=torch.int32)
-            _C.inf_dist_forward(x, weight, y, pos, group, ci, co)
+            if ascending and group == 1 and x.size(2) == 1 and (ci is not None or co is not None):
+                _C.inf_dist_forward_sorted(x, weight, y, pos, ci, co)
+            else:
+                _C.inf_dist_forward(x, weight, y, pos, group, ci, co)
             ctx.save_for_backward(x, weight, pos)
         else:
             _C.inf_dist_forward_nograd(x, weight, y, group)
@@ -101,14 +105,14 @@ class NormDistF(torch.autograd.Function):
 
 class NormDistDropoutF(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, w_index_ci, w_index_co, group, p, tag):
+    def forward(ctx, x, weight, w_index_ci, w_index_co, group, p, tag, ascending=False):
         assert weight.size(1) * group == x.size(1) or w_index_ci.size(-1) * group == x.size(1)
         ctx.tag = tag
-        return _dist_forward(ctx, x, weight, w_index_ci, w_index_co, group, p, True)
+        return _dist_forward(ctx, x, weight, w_index_ci, w_index_co, group, p, True, ascending)
 
     @staticmethod
     def backward(ctx, grad_output):
-        return _dist_backward(ctx, grad_output) + (None,) * 5
+        return _dist_backward(ctx, grad_output) + (None,) * 6
 
 
 class SortNeuronF(torch.autograd.Function):
@@ -212,7 +216,11 @@ class NormDistLayerF(torch.autograd.Function):
         pos = ws = mean = None
         if inf and (record or ci is not None or co is not None):
             pos = torch.empty(B, n_out, device=dev, dtype=torch.int32)
-            ws = torch.empty(B * n_out, device=dev, dtype=torch.int64)
+            if ci is None and co is None:
+                ws = torch.empty(B * n_out, device=dev, dtype=torch.int64)
+            else:           # merge keys + full-width input + inverse lists of the ascending-list form
+                nbytes = _lib.load().snb_inf_dist_forward_sorted_workspace_bytes(B, n_out, weight.size(1))
+                ws = torch.empty((nbytes + 7) // 8, device=dev, dtype=torch.int64)
         elif not inf and p > 10:
             ws = torch.empty(B * n_out, device=dev, dtype=torch.float32)
         if shift:
@@ -294,6 +302,13 @@ def norm_dist_dropout(input, weight, w_index_ci, w_index_co, p, groups=1, use_cu
     """`input` is already compact (dropped channels removed); `weight` is the full matrix."""
     _require_kernels(use_custom_cuda_func)
     return NormDistDropoutF.apply(input, weight, w_index_ci, w_index_co, groups, p, tag)
+
+
+def norm_dist_dropout_ascending(input, weight, w_index_ci, w_index_co, p, groups=1, tag=None):
+    """norm_dist_dropout for index lists in ascending order (sample_mask's, and the reference
+    sampler's: core/models/norm_dist.py:14-17): same results; the l-inf forward reads W along whole
+    rows (norm_dist_cuda.inf_dist_forward_sorted).  No counterpart in the reference."""
+    return NormDistDropoutF.apply(input, weight, w_index_ci, w_index_co, groups, p, tag, True)
 
 
 def _sort_is_plain_max(weight, q, truncate):

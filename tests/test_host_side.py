@@ -33,12 +33,15 @@ def test_loader_signatures_cover_the_header(built_lib):
     from sortnet_b200 import _lib
     utility = {"snb_status_string", "snb_last_cuda_error", "snb_version", "snb_inf_dist_forward_workspace_bytes",
                "snb_inf_dist_forward_noalloc_max_outputs", "snb_device_wait_failed", "snb_trim_scratch",
-               "snb_norm_dist_forward_workspace_bytes"}
+               "snb_norm_dist_forward_workspace_bytes", "snb_inf_dist_forward_sorted_workspace_bytes"}
     assert set(_lib.SIGNATURES) | utility == set(declared_symbols())
     lib = _lib.load()
     assert lib.snb_version() >= 100
     assert lib.snb_status_string(0) == b"ok" and b"null" in lib.snb_status_string(1)
     assert lib.snb_inf_dist_forward_workspace_bytes(512, 5120) == 8 * 512 * 5120
+    # merge keys + full-width input + one inverse list per 32-row sub-batch
+    assert lib.snb_inf_dist_forward_sorted_workspace_bytes(512, 4600, 5120) == 8 * 512 * 4600 + 4 * 512 * 5120 + 4 * 16 * 5120
+    assert lib.snb_inf_dist_forward_sorted_workspace_bytes(33, 3, 8) == 800 + 4 * 33 * 8 + 4 * 2 * 8   # 792 rounded up to 16
 
 
 def test_status_codes_without_gpu(built_lib):

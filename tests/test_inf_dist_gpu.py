@@ -95,6 +95,56 @@ def test_masked_vs_oracle(B, CI, CO, keep, which):
     assert rel(gx, gx_o) < 1e-5 and rel(gw, gw_o) < 1e-5
 
 
+def run_forward_sorted(x, w, ci=None, co=None):
+    from sortnet_b200 import norm_dist_cuda as C
+    CO = co.shape[-1] if co is not None else w.shape[0]
+    y = torch.full((x.shape[0], CO, 1), float("nan"), device="cuda")
+    pos = torch.full_like(y, -7, dtype=torch.int32)
+    C.inf_dist_forward_sorted(col3(x), dev(w), y, pos, idx3(ci), idx3(co))
+    return host(y), host(pos)
+
+
+# full-width form (W_CI a multiple of 4, >= 3/4 of the columns kept) and the cases that fall back
+# to the general masked path (few columns kept, odd W_CI); ragged last sub-batch and tile edges
+@pytest.mark.parametrize("B,CI,CO,keep", [(70, 48, 40, 0.8), (96, 300, 520, 0.9), (33, 72, 90, 0.5),
+                                          (160, 1032, 260, 0.9), (32, 64, 64, 1.0), (100, 131, 70, 0.9),
+                                          (512, 1280, 1100, 0.9)])
+@pytest.mark.parametrize("which", ["both", "ci", "co"])
+@pytest.mark.parametrize("ties", [False, True])
+def test_sorted_lists_entry_vs_oracle(B, CI, CO, keep, which, ties):
+    """snb_inf_dist_forward_sorted_ws: y and pos bit-identical to the oracle, also when many
+    columns tie for the maximum (quantised operands), where the position must be the lowest one."""
+    rng = np.random.default_rng(B + CI + CO + (7 if ties else 0))
+    ci = make_masks(rng, B, CI, keep) if which in ("both", "ci") else None
+    co = make_masks(rng, B, CO, keep) if which in ("both", "co") else None
+    n_in = ci.shape[1] if ci is not None else CI
+    if ties:
+        x = (rng.integers(0, 4, (B, n_in)) / 4).astype(np.float32)
+        w = (rng.integers(-4, 5, (CO, CI)) / 4).astype(np.float32)
+    else:
+        x = rng.random((B, n_in), dtype=np.float32)
+        w = rng.standard_normal((CO, CI)).astype(np.float32)
+    y_o, pos_o = oracle.inf_dist_forward(x, w, ci, co)
+    y, pos = run_forward_sorted(x, w, ci, co)
+    assert np.array_equal(y, y_o) and np.array_equal(pos, pos_o)
+
+
+def test_sorted_lists_entry_all_equal_operands():
+    """x == w in every kept column: nothing exceeds 1e-10, y = 1e-10 and pos = 0 (as the reference);
+    the dropped columns' weights are huge and must not be seen."""
+    rng = np.random.default_rng(3)
+    B, CI, CO = 64, 128, 96
+    ci = make_masks(rng, B, CI, 0.8)
+    w = np.full((CO, CI), 1e6, np.float32)
+    x = np.full((B, ci.shape[1]), 0.5, np.float32)
+    for s in range(ci.shape[0]):
+        w[:, ci[s]] = 0.5
+    y_o, pos_o = oracle.inf_dist_forward(x, w, ci, None)
+    y, pos = run_forward_sorted(x, w, ci, None)
+    assert np.array_equal(y, y_o) and np.array_equal(pos, pos_o)
+    assert np.all(y == np.float32(1e-10)) and np.all(pos == 0)
+
+
 @pytest.mark.parametrize("B,CI,CO", [(128, 784, 5120), (512, 1024, 2100), (100, 130, 257)])
 def test_workspace_and_plain_entry_points_agree(B, CI, CO):
     """Unmasked forward through the C ABI three ways: without scratch, with scratch (tiles split
