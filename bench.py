@@ -678,7 +678,10 @@ def gpu_comparator_block(job, steps=10, warmup=3):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / n
 
-    ms_ref = timed(step, steps, warmup)
+    # the faster of two blocks: on a freshly started machine the first block still pages code of the
+    # PyTorch operators the reference's sampler uses in from disk (seen: 125-180 ms against 40 ms)
+    ms_blocks = [timed(step, steps, warmup), timed(step, steps, 0)]
+    ms_ref = min(ms_blocks)
     ms_ref_faithful = timed(lambda x, t: bound_pass(x, t, True), 3, 1)
     with torch.no_grad():
         ms_ours_faithful = timed(lambda x, t: job.model.certified_margin(x, t, eps, job.up, job.down), 3, 1)
@@ -688,6 +691,7 @@ def gpu_comparator_block(job, steps=10, warmup=3):
     return {"what": "configs[1] step through the reference's SortMLPModel + core/norm_dist.py over its own CUDA "
                     "extension built for sm_100a, torch.optim.AdamW, l-inf bound pass via its keep-rate-1 branch",
             "ms_per_step": round(ms_ref, 3), "samples_per_s": round(job.B / (ms_ref * 1e-3), 1), "steps": steps,
+            "ms_per_step_blocks": [round(v, 3) for v in ms_blocks],
             "eval_faithful_bound_pass": {"what": "evaluation forward with the sort neuron and its bounds (K = 10), no grad",
                                          "reference_ms": round(ms_ref_faithful, 3), "ours_ms": round(ms_ours_faithful, 3),
                                          "speedup": round(ms_ref_faithful / ms_ours_faithful, 3)}}
