@@ -752,7 +752,34 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    job.run(args.warmup)
+    # Warm-up.  A peer-memory exchange that fails here with an error the process survives (a rank
+    # whose GPU-side wait for a peer ran into its time limit raises from FlatAdamW.check()) makes
+    # all ranks start over with one NCCL all-reduce per step; the JSON line says so.
+    fallback = None
+    try:
+        job.run(args.warmup)
+        torch.cuda.synchronize()
+        if world > 1:
+            job.opt.check()
+            if args.inject_exchange_failure and rank == world - 1:
+                raise RuntimeError("injected on the host by --inject-exchange-failure")
+    except RuntimeError as exc:
+        if world == 1 or exchange == "nccl":
+            raise
+        fallback = str(exc).splitlines()[0][:200]
+        print("rank %d: %s exchange failed in warm-up (%s)" % (rank, exchange, fallback), file=sys.stderr)
+    if world > 1 and exchange != "nccl":
+        flag = torch.tensor([1.0 if fallback else 0.0], device=dev)
+        dist.all_reduce(flag)
+        if float(flag) > 0:
+            torch.cuda.synchronize()
+            job.release()
+            fallback = fallback or "another rank's exchange failed"
+            exchange = "nccl"
+            exchange_text = ("one flat NCCL all-reduce + local fused AdamW (the peer-memory exchange failed in "
+                             "warm-up: %s)" % fallback)
+            job = Job(HEADLINE, dev, world, rank, exchange=exchange)
+            job.run(args.warmup)
     barrier()
 
     # ---- timed region 1: inputs resident in HBM, no per-call events ---------------------
@@ -953,6 +980,9 @@ def main():
                     help="gradient exchange at N > 1 (default: overlapped device-to-device copies)")
     ap.add_argument("--configs4", action="store_true", help="run the configs[4] block (width 10240, 128 rows per GPU) at "
                                                            "this N > 1 as well; by default it runs at N = 8 only")
+    ap.add_argument("--inject-exchange-failure", action="store_true",
+                    help="N > 1: the last rank raises on the host after the warm-up, as if its exchange had failed, "
+                         "to exercise the switch to the NCCL exchange")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary blocks (other configurations, finite p, "
                                                               "GPU comparator)")
