@@ -65,7 +65,14 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
     "snb_bound_inf_dist_forward_nograd": 302.8e6,
     "snb_inf_dist_forward_ws": 262.2e6,
     "snb_inf_dist_forward_sorted_ws": 266.2e6,
+    "snb_inf_dist_forward_nograd": 203.9e6,       # inf_fwd_sk_kernel_dense_512x5120x5120.md
 }
+
+
+# adamw_kernel: 480.0 MB read + 302.2-304.4 MB written per launch on 30 M parameters (ncu, the capture
+# of profiles/adamw_kernel_30m_parameters.md; the last writes are still in L2 when the kernel ends);
+# traffic grows in proportion to the parameter count
+NCU_ADAMW_BYTES_PER_PARAMETER = 26.1
 
 
 def layer_dims(cfg):
@@ -561,7 +568,8 @@ def hbm_block(job):
     adam_gbs = 28.0 * opt.numel / (adam_ms * 1e-3) * 1e-9
     return {"bound": "hbm", "kernel": "adamw_kernel", "ms_per_launch": round(adam_ms, 4),
             "achieved": round(adam_gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(adam_gbs / hbm_peak, 4),
-            "traffic": None, "algorithmic_bytes": 28 * opt.numel, "peak_source": hbm_src}
+            "traffic": round(NCU_ADAMW_BYTES_PER_PARAMETER * opt.numel), "algorithmic_bytes": 28 * opt.numel,
+            "peak_source": hbm_src}
 
 
 def single_layer_block(dev, peak_gflops):

@@ -5,7 +5,8 @@
 Used for quick timing of a single kernel and as the small, self-terminating command that
 profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_fwd_sorted (its ascending-list form), inf_nograd,
 inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_shift, sort_nograd,
-sort_bound, sort_fwd (values + positions), sort_bwd (K = 10, q = 0.9), probe (hardware probes).
+sort_bound, sort_fwd (values + positions), sort_bwd (K = 10, q = 0.9), adamw (the fused optimiser kernel on
+--n parameters), probe (hardware probes).
 """
 import argparse
 import ctypes
@@ -75,6 +76,31 @@ def probe():
               % (v, name, ms, elems / (ms * 1e-3) / clk / sms, 128.0 / (elems / (ms * 1e-3) / clk / sms)))
 
 
+def adamw(a, dev):
+    """The fused flat-buffer AdamW kernel alone on --n parameters (28 bytes of traffic each)."""
+    lib = _lib.load()
+    n = a.n // 4 * 4
+    param, grad = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def run(step):
+        _lib.check(lib.snb_adamw_step(param.data_ptr(), grad.data_ptr(), m.data_ptr(), v.data_ptr(), n, 0.02, 0.9,
+                                      0.99, 1e-10, 0.0, step, 1.0, stream), "adamw_step")
+
+    for i in range(a.warmup):
+        run(1 + i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.iters):
+        run(1 + a.warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.iters
+    print("adamw n=%d: %.4f ms  %.1f GB/s (28 bytes / parameter)" % (n, ms, 28.0 * n / ms * 1e-6))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True)
@@ -83,6 +109,7 @@ def main():
     ap.add_argument("--CO", type=int, default=5120)
     ap.add_argument("--keep", type=float, default=1.0)
     ap.add_argument("--p", type=float, default=8.0)
+    ap.add_argument("--n", type=int, default=30_000_000, help="adamw: number of parameters")
     ap.add_argument("--mask", choices=("both", "ci", "co"), default="both",
                     help="with --keep < 1: which index lists to draw (co = kept rows of W only, like a first layer)")
     ap.add_argument("--iters", type=int, default=5)
@@ -98,6 +125,8 @@ def main():
         return probe()
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
+    if a.op == "adamw":
+        return adamw(a, dev)
     S = (a.B + 31) // 32
     ci = co = None
     if a.keep < 1.0:
