@@ -6,7 +6,7 @@ Used for quick timing of a single kernel and as the small, self-terminating comm
 profilers attach to.  Ops: inf_fwd (argmax words; masked when --keep < 1), inf_fwd_sorted (its ascending-list form), inf_nograd,
 inf_bwd, bound_nograd, bound_fwd, lp_fwd, lp_bwd, lp_bwd_x (grad_x only), mean_shift, sort_nograd,
 sort_bound, sort_fwd (values + positions), sort_bwd (K = 10, q = 0.9), adamw (the fused optimiser kernel on
---n parameters), probe (hardware probes).
+--n parameters), bound_pass_update (the model's bound pass with the optimiser update beside it), probe (hardware probes).
 """
 import argparse
 import ctypes
@@ -101,6 +101,53 @@ def adamw(a, dev):
     print("adamw n=%d: %.4f ms  %.1f GB/s (28 bytes / parameter)" % (n, ms, 28.0 * n / ms * 1e-6))
 
 
+def bound_pass_update(a, dev):
+    """The interval-bound pass of the headline model with the single-GPU optimiser update (sum of one
+    gradient part + AdamW into a second parameter buffer, 120.6 M parameters) launched after its second
+    layer: --update none | main (same stream) | side (another stream)."""
+    import bench
+    lib = _lib.load()
+    job = bench.Job(bench.HEADLINE, dev, 1, 0, exchange="none")
+    job.run(3)
+    x, t = job.dev_x[0], job.dev_t[0]
+    n = job.opt.numel
+    src = job.opt.flat_param
+    dst, grad = torch.empty_like(src), torch.randn(n, device=dev) * 1e-3
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    side = torch.cuda.Stream()
+    parts = (ctypes.c_void_p * 1)(grad.data_ptr())
+    bound_ms = update_ms = 0.0
+    for it in range(a.iters + a.warmup):
+        main = torch.cuda.current_stream()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ready = torch.cuda.Event()
+
+        def hook(k):
+            if k != 1 or a.update == "none":
+                return
+            stream = main
+            if a.update == "side":
+                ready.record(main)
+                side.wait_event(ready)
+                stream = side
+            e[2].record(stream)
+            _lib.check(lib.snb_adamw_reduce_step(src.data_ptr(), dst.data_ptr(), parts, 1, m.data_ptr(), v.data_ptr(), n,
+                                                 0.02, 0.9, 0.99, 1e-10, 0.0, it + 1, 1.0, stream.cuda_stream), "adamw")
+            e[3].record(stream)
+
+        e[0].record()
+        job.bound_pass(x, t, after_layer=hook)
+        e[1].record()
+        main.wait_stream(side)
+        torch.cuda.synchronize()
+        if it >= a.warmup:
+            bound_ms += e[0].elapsed_time(e[1])
+            if a.update != "none":
+                update_ms += e[2].elapsed_time(e[3])
+    print("bound pass with the update on '%s': %.3f ms, update kernel %.3f ms" % (a.update, bound_ms / a.iters,
+                                                                                 update_ms / a.iters))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True)
@@ -110,6 +157,8 @@ def main():
     ap.add_argument("--keep", type=float, default=1.0)
     ap.add_argument("--p", type=float, default=8.0)
     ap.add_argument("--n", type=int, default=30_000_000, help="adamw: number of parameters")
+    ap.add_argument("--update", choices=("none", "main", "side"), default="side",
+                    help="bound_pass_update: where the optimiser update is launched")
     ap.add_argument("--mask", choices=("both", "ci", "co"), default="both",
                     help="with --keep < 1: which index lists to draw (co = kept rows of W only, like a first layer)")
     ap.add_argument("--iters", type=int, default=5)
@@ -127,6 +176,8 @@ def main():
     torch.manual_seed(0)
     if a.op == "adamw":
         return adamw(a, dev)
+    if a.op == "bound_pass_update":
+        return bound_pass_update(a, dev)
     S = (a.B + 31) // 32
     ci = co = None
     if a.keep < 1.0:
