@@ -258,6 +258,13 @@ int snb_mean_shift_apply(const float* x, const float* mean, const int* index, in
  * tensor shapes. */
 int snb_sample_mask(int* out, int lists, int channels, int count, unsigned long long seed, void* stream);
 
+/* `jobs` (<= 16) calls of snb_sample_mask in one launch, e.g. the masks of every layer of a model for
+ * one training step: outs[j] [lists, counts[j]] receives the lists that
+ * snb_sample_mask(outs[j], lists, channels[j], counts[j], seeds[j]) would write.  outs, channels,
+ * counts and seeds are host arrays of `jobs` entries.  No counterpart in the reference. */
+int snb_sample_mask_batch(int jobs, int* const* outs, const int* channels, const int* counts,
+                          const unsigned long long* seeds, int lists, void* stream);
+
 /* Debug aid: checks caller-made index lists (index [lists, count] int32, i.e. the [S, G, count] lists
  * of one operand) before they are handed to the kernels, which read w through them unchecked like
  * the reference's (inf_dist_cuda.cu:163-172).  Returns SNB_STATUS_INDEX_RANGE when an entry lies

@@ -37,6 +37,7 @@ SIGNATURES = {
     "snb_mean_shift_stats": [_P, _P, _I, _I, _I, _P, _P, _F, _P],
     "snb_mean_shift_apply": [_P, _P, _P, _I, _I, _P, _P],
     "snb_sample_mask": [_P, _I, _I, _I, ctypes.c_ulonglong, _P],
+    "snb_sample_mask_batch": [_I, _P, _P, _P, _P, _I, _P],
     "snb_adamw_step": [_P, _P, _P, _P, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _F, _P],
     "snb_adamw_reduce_step": [_P, _P, _P, _I, _P, _P, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _F, _P],
     "snb_dp_adamw_step": [_P, _P, _P, _P, _I, _I, ctypes.c_longlong, ctypes.c_longlong, _F, _F, _F, _F, _F, _I, _P],

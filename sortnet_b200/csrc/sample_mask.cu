@@ -65,15 +65,17 @@ __device__ __forceinline__ int cta_exclusive_scan(int v, int* warp_sums, int* to
     return r;
 }
 
-__global__ void __launch_bounds__(SM_THREADS) sample_mask_kernel(int* __restrict__ out, int channels, int count,
-                                                                 uint32_t seed_lo, uint32_t seed_hi) {
+// One list by one CTA (see the file header); `list` is the list's number within its call, which
+// enters the random counter.
+__device__ __forceinline__ void sample_one_list(int* __restrict__ out, int channels, int count, uint32_t seed_lo,
+                                                uint32_t seed_hi, int list) {
     extern __shared__ uint32_t keys[];  // [channels rounded up to 4]
     __shared__ int hist[256];
     __shared__ int warp_sums[SM_THREADS / 32];
     __shared__ int s_total;
     __shared__ uint32_t s_prefix;
     __shared__ int s_need;
-    const int tid = threadIdx.x, list = blockIdx.x;
+    const int tid = threadIdx.x;
     for (int q = tid; q * 4 < channels; q += SM_THREADS) {
         uint32_t c[4] = {(uint32_t)q, (uint32_t)list, 0u, 0u};
         philox4x32_10(c, seed_lo, seed_hi);
@@ -134,6 +136,41 @@ __global__ void __launch_bounds__(SM_THREADS) sample_mask_kernel(int* __restrict
     }
 }
 
+__global__ void __launch_bounds__(SM_THREADS) sample_mask_kernel(int* __restrict__ out, int channels, int count,
+                                                                 uint32_t seed_lo, uint32_t seed_hi) {
+    sample_one_list(out, channels, count, seed_lo, seed_hi, blockIdx.x);
+}
+
+// Several independent calls of the kernel above in one launch (the masks of all layers of a model
+// for one step): CTA b makes list b % lists of job b / lists, with that job's seed, so every job's
+// lists are the ones its own snb_sample_mask call would have produced.
+constexpr int SAMPLE_MAX_JOBS = 16;
+struct SampleJobs {
+    int* out[SAMPLE_MAX_JOBS];
+    int channels[SAMPLE_MAX_JOBS];
+    int count[SAMPLE_MAX_JOBS];
+    uint32_t seed_lo[SAMPLE_MAX_JOBS];
+    uint32_t seed_hi[SAMPLE_MAX_JOBS];
+};
+
+__global__ void __launch_bounds__(SM_THREADS) sample_mask_batch_kernel(const SampleJobs jobs, int lists) {
+    const int job = blockIdx.x / lists, list = blockIdx.x % lists;
+    // compile-time indices keep the job table in the parameter bank
+    int* out = nullptr;
+    int channels = 0, count = 0;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < SAMPLE_MAX_JOBS; j++)
+        if (j == job) {
+            out = jobs.out[j];
+            channels = jobs.channels[j];
+            count = jobs.count[j];
+            lo = jobs.seed_lo[j];
+            hi = jobs.seed_hi[j];
+        }
+    sample_one_list(out, channels, count, lo, hi, list);
+}
+
 // Validation of caller-made index lists (debug aid): bit 0 = an entry outside [0, channels),
 // bit 1 = a list that is not strictly ascending.
 __device__ int snb_index_check_bits;
@@ -172,19 +209,54 @@ extern "C" int snb_check_index_lists(const int* index, int lists, int count, int
     return (bits & 1) ? SNB_ERR_INDEX_RANGE : SNB_OK;
 }
 
+static int configure_sampler() {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    SNB_CUDA(cudaGetDevice(&dev));
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
+        SNB_CUDA(cudaFuncSetAttribute(sample_mask_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        SNB_CUDA(cudaFuncSetAttribute(sample_mask_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured[dev & 63].store(true, std::memory_order_release);
+    }
+    return SNB_OK;
+}
+
+// `jobs` calls of snb_sample_mask in one launch: outs[j] receives `lists` lists of counts[j] kept
+// channels out of channels[j], drawn with seeds[j] (host arrays).  Same lists as the separate calls.
+extern "C" int snb_sample_mask_batch(int jobs, int* const* outs, const int* channels, const int* counts,
+                                     const unsigned long long* seeds, int lists, void* stream) {
+    if (!outs || !channels || !counts || !seeds) return SNB_ERR_NULL_POINTER;
+    if (jobs <= 0 || lists <= 0) return SNB_ERR_BAD_SHAPE;
+    if (jobs > SAMPLE_MAX_JOBS) return SNB_ERR_UNSUPPORTED;
+    SampleJobs table{};
+    size_t smem = 0;
+    for (int j = 0; j < jobs; j++) {
+        if (!outs[j]) return SNB_ERR_NULL_POINTER;
+        if (channels[j] <= 0 || counts[j] <= 0 || counts[j] > channels[j]) return SNB_ERR_BAD_SHAPE;
+        const size_t need = sizeof(uint32_t) * (size_t)((channels[j] + 3) / 4 * 4);
+        if (need > 200 * 1024) return SNB_ERR_TOO_LARGE;
+        smem = need > smem ? need : smem;
+        table.out[j] = outs[j];
+        table.channels[j] = channels[j];
+        table.count[j] = counts[j];
+        table.seed_lo[j] = (uint32_t)seeds[j];
+        table.seed_hi[j] = (uint32_t)(seeds[j] >> 32);
+    }
+    int rc = configure_sampler();
+    if (rc) return rc;
+    sample_mask_batch_kernel<<<jobs * lists, SM_THREADS, smem, (cudaStream_t)stream>>>(table, lists);
+    SNB_CUDA(cudaGetLastError());
+    return SNB_OK;
+}
+
 extern "C" int snb_sample_mask(int* out, int lists, int channels, int count, unsigned long long seed,
                                void* stream) {
     if (!out) return SNB_ERR_NULL_POINTER;
     if (lists <= 0 || channels <= 0 || count <= 0 || count > channels) return SNB_ERR_BAD_SHAPE;
     const size_t smem = sizeof(uint32_t) * (size_t)((channels + 3) / 4 * 4);
     if (smem > 200 * 1024) return SNB_ERR_TOO_LARGE;  // 51200 channels
-    static std::atomic<bool> configured[64];
-    int dev = 0;
-    SNB_CUDA(cudaGetDevice(&dev));
-    if (!configured[dev & 63].load(std::memory_order_acquire)) {
-        SNB_CUDA(cudaFuncSetAttribute(sample_mask_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured[dev & 63].store(true, std::memory_order_release);
-    }
+    int rc = configure_sampler();
+    if (rc) return rc;
     sample_mask_kernel<<<lists, SM_THREADS, smem, (cudaStream_t)stream>>>(out, channels, count, (uint32_t)seed,
                                                                          (uint32_t)(seed >> 32));
     SNB_CUDA(cudaGetLastError());

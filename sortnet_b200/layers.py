@@ -409,6 +409,17 @@ class SortMLPModel(nn.Module):
         # would cost a device synchronisation per step and stop the host from queueing kernels
         # ahead of the GPU.
         counts = [int((torch.rand(l.in_features) < l.keep_rate).sum()) for _, l in todo]
+        device = torch.device(device)
+        if device.type == "cuda" and 1 < len(todo) <= 16:
+            # all layers' lists in one launch; counts, seeds and lists are those of the per-layer calls
+            outs, seeds = [], []
+            for (k, l), c in zip(todo, counts):
+                c = min(max(int(c), 1), l.in_features)
+                seeds.append(int(torch.randint(0, 2 ** 62, (1,))))
+                outs.append(torch.empty(sub, 1, c, dtype=torch.int32, device=device))
+                masks[k] = outs[-1]
+            _C.sample_masks_into(outs, [l.in_features for _, l in todo], seeds)
+            return masks
         for (k, l), c in zip(todo, counts):
             masks[k] = sample_mask(sub, 1, l.in_features, l.keep_rate, device, count=max(int(c), 1))
         return masks

@@ -14,6 +14,7 @@ outside [0, channels) raises.
 `install()` registers this module as `norm_dist_cuda` in sys.modules so that the reference's
 unmodified `core/norm_dist.py` (`import norm_dist_cuda as _C`) runs on these kernels.
 """
+import ctypes
 import os
 import sys
 
@@ -78,7 +79,7 @@ _KERNELS = {
     "snb_inf_dist_backward_input_weight": 1, "snb_norm_dist_forward": 1, "snb_norm_dist_forward_ws": 2, "snb_norm_dist_backward_input": 1,
     "snb_norm_dist_backward_input_weight": 1, "snb_bound_inf_dist_forward_nograd": 1,
     "snb_bound_inf_dist_forward": 1, "snb_bound_inf_dist_backward_input": 1,
-    "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1, "snb_sample_mask": 1,
+    "snb_bound_inf_dist_backward_input_weight": 1, "snb_mean_shift_stats": 1, "snb_mean_shift_apply": 1, "snb_sample_mask": 1, "snb_sample_mask_batch": 1,
     "snb_sort_neuron_forward_nograd": 1, "snb_sort_neuron_forward": 1, "snb_bound_sort_neuron_forward": 1,
     "snb_sort_neuron_backward_input": 1, "snb_sort_neuron_backward_input_weight": 1,
 }
@@ -435,6 +436,25 @@ def sample_mask_into(out, channels, seed):
     lists, count = out.size(0) * out.size(1), out.size(2)
     _call(out.device, out, "snb_sample_mask", (lists, channels, count),
           _ptr(out), lists, int(channels), count, int(seed) & 0xFFFFFFFFFFFFFFFF)
+
+
+def sample_masks_into(outs, channels, seeds):
+    """sample_mask_into for several tensors in one launch: outs[j] [S, G, count_j] int32 (the same
+    S * G for all), channels[j], seeds[j].  Same lists as separate sample_mask_into calls."""
+    if not outs or len(outs) != len(channels) or len(outs) != len(seeds):
+        raise RuntimeError("outs, channels and seeds must be non-empty and of equal length")
+    lists = outs[0].size(0) * outs[0].size(1)
+    for out in outs:
+        _check(out, "out", torch.int32)
+        if out.dim() != 3 or out.size(0) * out.size(1) != lists or out.device != outs[0].device:
+            raise RuntimeError("every out must be [sub-batches, groups, count] with the same number of lists on one device")
+    n = len(outs)
+    ptrs = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+    chans = (ctypes.c_int * n)(*[int(c) for c in channels])
+    counts = (ctypes.c_int * n)(*[o.size(2) for o in outs])
+    seed_arr = (ctypes.c_ulonglong * n)(*[int(s) & 0xFFFFFFFFFFFFFFFF for s in seeds])
+    _call(outs[0].device, outs[0], "snb_sample_mask_batch", (n, lists, max(int(c) for c in channels)),
+          n, ptrs, chans, counts, seed_arr, lists)
 
 
 # ---- whole layers and the model head (one C call each; G = 1, HW = 1, 2-D tensors) ---------------

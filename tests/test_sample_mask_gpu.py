@@ -81,6 +81,38 @@ def test_layer_level_sampler_is_reproducible_and_sorted():
     assert c.shape == (4, 2, 17)
 
 
+def test_batched_launch_writes_the_lists_of_the_separate_calls():
+    """snb_sample_mask_batch: several (channels, count, seed) jobs in one launch, each bit-identical to
+    its own snb_sample_mask call and to the restated algorithm."""
+    from sortnet_b200 import norm_dist_cuda as C
+    jobs = [(3072, 2750, 11), (5120, 4608, 12), (5120, 4590, 13), (40, 1, 14), (12288, 11000, 15)]
+    S = 16
+    outs = [torch.full((S, 1, count), -1, dtype=torch.int32, device="cuda") for _, count, _ in jobs]
+    C.sample_masks_into(outs, [ch for ch, _, _ in jobs], [seed for _, _, seed in jobs])
+    for out, (channels, count, seed) in zip(outs, jobs):
+        assert np.array_equal(out.cpu().numpy(), draw(S, 1, channels, count, seed))
+        assert np.array_equal(out.cpu().numpy().reshape(S, count), expected_lists(S, channels, count, seed))
+    with pytest.raises(RuntimeError):
+        C.sample_masks_into(outs[:2], [3072], [1, 2])
+    with pytest.raises(RuntimeError):
+        C.sample_masks_into([outs[0]] * 17, [3072] * 17, list(range(17)))    # more jobs than one launch takes
+
+
+def test_model_masks_are_the_same_through_either_route():
+    """SortMLPModel.draw_masks (one launch for all layers) against per-layer sample_mask calls with
+    the same generator state."""
+    from sortnet_b200 import layers
+    model = layers.SortMLPModel(depth=4, width=256, input_dim=(1, 8, 8), num_classes=10, dropout=0.9).cuda()
+    torch.manual_seed(21)
+    batched = model.draw_masks(96, "cuda")
+    torch.manual_seed(21)
+    todo = [(k, l) for k, l in enumerate(model.fc_dist[1:]) if l.keep_rate != 1.0]
+    counts = [int((torch.rand(l.in_features) < l.keep_rate).sum()) for _, l in todo]
+    for (k, l), c in zip(todo, counts):
+        single = layers.sample_mask(3, 1, l.in_features, l.keep_rate, "cuda", count=max(c, 1))
+        assert torch.equal(batched[k], single)
+
+
 def test_bad_arguments():
     from sortnet_b200 import norm_dist_cuda as C
     out = torch.empty(2, 1, 10, dtype=torch.int32, device="cuda")
