@@ -56,34 +56,66 @@ __global__ void __launch_bounds__(256) shift_bias3_kernel(float* __restrict__ y,
 }
 
 // sum[c] = sum over the rows whose sub-batch kept channel c of g[b, slot(c)] (bias gradient).
-// Fixed summation order: rows ascending inside a sub-batch, sub-batches ascending.
+// Fixed summation order: rows ascending inside a sub-batch, then the sub-batches' partial sums
+// ascending.  CTA = 16 channels x 16 lanes; lane sg takes the sub-batches sg, sg + 16, ..., leaves
+// their partial sums in shared memory, and lane 0 adds them in order (up to COLSUM_MAX_S
+// sub-batches; beyond that the partial sums are added as they come, by one thread per channel).
+constexpr int COLSUM_MAX_S = 64;
+
+__device__ __forceinline__ float column_part(const float* __restrict__ g, const int* __restrict__ index, int B, int C,
+                                             int c, int s, bool* kept) {
+    int slot = c;
+    if (index) {
+        const int* idx = index + (size_t)s * C;
+        int lo = 0, hi = C;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (idx[mid] < c) lo = mid + 1;
+            else hi = mid;
+        }
+        slot = (lo < C && idx[lo] == c) ? lo : -1;
+    } else if (c >= C) {
+        slot = -1;
+    }
+    *kept = slot >= 0;
+    if (slot < 0) return 0.f;
+    const int b0 = s * SNB_SUB_BATCH, b1 = min(B, b0 + SNB_SUB_BATCH);
+    float part = 0.f;
+    for (int b = b0; b < b1; b++) part += g[(size_t)b * C + slot];
+    return part;
+}
+
 __global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ g, const int* __restrict__ index,
                                                          int B, int C, int C_full, float* __restrict__ sum) {
-    const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= C_full) return;
+    __shared__ float parts[COLSUM_MAX_S][17];
+    __shared__ unsigned char have[COLSUM_MAX_S][17];
+    const int cx = threadIdx.x & 15, sg = threadIdx.x >> 4;
+    const int c = blockIdx.x * 16 + cx;
     const int S = (B + SNB_SUB_BATCH - 1) / SNB_SUB_BATCH;
-    float total = 0.f;
-    for (int s = 0; s < S; s++) {
-        int slot = c;
-        if (index) {
-            const int* idx = index + (size_t)s * C;
-            int lo = 0, hi = C;
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if (idx[mid] < c) lo = mid + 1;
-                else hi = mid;
-            }
-            slot = (lo < C && idx[lo] == c) ? lo : -1;
-        } else if (c >= C) {
-            slot = -1;
+    if (S > COLSUM_MAX_S) {
+        if (sg != 0 || c >= C_full) return;
+        float total = 0.f;
+        for (int s = 0; s < S; s++) {
+            bool kept;
+            const float part = column_part(g, index, B, C, c, s, &kept);
+            if (kept) total += part;
         }
-        if (slot < 0) continue;
-        const int b0 = s * SNB_SUB_BATCH, b1 = min(B, b0 + SNB_SUB_BATCH);
-        float part = 0.f;
-        for (int b = b0; b < b1; b++) part += g[(size_t)b * C + slot];
-        total += part;
+        sum[c] = total;
+        return;
     }
-    sum[c] = total;
+    if (c < C_full)
+        for (int s = sg; s < S; s += 16) {
+            bool kept;
+            parts[s][cx] = column_part(g, index, B, C, c, s, &kept);
+            have[s][cx] = kept;
+        }
+    __syncthreads();
+    if (sg == 0 && c < C_full) {
+        float total = 0.f;
+        for (int s = 0; s < S; s++)
+            if (have[s][cx]) total += parts[s][cx];
+        sum[c] = total;
+    }
 }
 
 // lower = max(x - eps, down), upper = min(x + eps, up) (ell_inf_models.py:35-36 with scalar bounds).
@@ -247,7 +279,7 @@ extern "C" int snb_layer_backward(const float* grad_out, const float* x, const f
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if (grad_bias) {
-        column_sum_kernel<<<(W_CO + 255) / 256, 256, 0, st>>>(grad_out, w_index_co, B, CO, W_CO, grad_bias);
+        column_sum_kernel<<<(W_CO + 15) / 16, 256, 0, st>>>(grad_out, w_index_co, B, CO, W_CO, grad_bias);
         SNB_CUDA(cudaGetLastError());
     }
     const float* g = grad_out;
