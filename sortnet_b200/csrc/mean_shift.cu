@@ -16,21 +16,23 @@
 
 namespace snb {
 
-// CTA = 32 channels x 8 sub-batch lanes.  Lane (cx, sg) sums channel c over the sub-batches
-// sg, sg + 8, ...; the 8 partial sums are then added in index order.
+// CTA = 16 channels x 16 sub-batch lanes.  Lane (cx, sg) sums channel c over the sub-batches
+// sg, sg + 16, ...; the 16 partial sums are then added in index order.  The kernel is bound by the
+// latency of each lane's chain (a binary search in the sorted list, then 32 rows), hence many short
+// chains.
 __global__ void __launch_bounds__(256) mean_shift_stats_kernel(const float* __restrict__ x,
                                                                const int* __restrict__ index, int B,
                                                                int C, int C_full, float* __restrict__ mean,
                                                                float* __restrict__ running_mean,
                                                                float momentum) {
-    __shared__ float ssum[8][33];
-    __shared__ float scnt[8][33];
-    const int cx = threadIdx.x & 31, sg = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cx;
+    __shared__ float ssum[16][17];
+    __shared__ float scnt[16][17];
+    const int cx = threadIdx.x & 15, sg = threadIdx.x >> 4;
+    const int c = blockIdx.x * 16 + cx;
     const int S = (B + SNB_SUB_BATCH - 1) / SNB_SUB_BATCH;
     float sum = 0.f, cnt = 0.f;
     if (c < C_full) {
-        for (int s = sg; s < S; s += 8) {
+        for (int s = sg; s < S; s += 16) {
             int slot = c;
             if (index) {
                 // lower bound of c in the sorted kept-channel list of sub-batch s
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(256) mean_shift_stats_kernel(const float* __re
     if (sg == 0 && c < C_full) {
         float t = 0.f, n = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
+        for (int k = 0; k < 16; k++) {
             t += ssum[k][cx];
             n += scnt[k][cx];
         }
@@ -90,7 +92,7 @@ extern "C" int snb_mean_shift_stats(const float* x, const int* index, int B, int
     if (!x || !mean) return SNB_ERR_NULL_POINTER;
     if (B <= 0 || C <= 0 || C_full < C || (!index && C_full != C)) return SNB_ERR_BAD_SHAPE;
     if ((long long)B * C >= (1ll << 31)) return SNB_ERR_TOO_LARGE;
-    mean_shift_stats_kernel<<<(C_full + 31) / 32, 256, 0, (cudaStream_t)stream>>>(
+    mean_shift_stats_kernel<<<(C_full + 15) / 16, 256, 0, (cudaStream_t)stream>>>(
         x, index, B, C, C_full, mean, running_mean, momentum);
     SNB_CUDA(cudaGetLastError());
     return SNB_OK;
