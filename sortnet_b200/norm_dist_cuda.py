@@ -170,6 +170,10 @@ def inf_dist_forward_sorted(input, weight, output, pos, w_index_ci=None, w_index
     if output.size(0) != B or pos.shape != output.shape:
         raise RuntimeError("output / pos shape mismatch")
     dev = _same_device(input, weight, output, pos, w_index_ci, w_index_co)
+    if DEBUG_INDEX_CHECKS:        # the promise itself: every list strictly ascending
+        for t, name, channels in ((w_index_ci, "w_index_ci", weight.size(1)), (w_index_co, "w_index_co", weight.size(0))):
+            if t is not None and not check_index_lists(t, channels, name):
+                raise RuntimeError("%s is not in ascending order: use inf_dist_forward" % name)
     nbytes = _lib.load().snb_inf_dist_forward_sorted_workspace_bytes(B, CO, weight.size(1))
     ws = torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=dev)
     _call(dev, input, "snb_inf_dist_forward_sorted_ws", (B, CO, CI),

@@ -155,3 +155,8 @@ def test_debug_mode_validates_index_lists_before_the_kernels(monkeypatch):
     bad_co = torch.tensor([[[1, 6]]], dtype=torch.int32, device="cuda")         # w has 6 rows
     with pytest.raises(RuntimeError, match="w_index_co"):
         C.inf_dist_forward(x, w, y, pos, 1, ci, bad_co)
+    # the ascending-list entry also checks its promise
+    C.inf_dist_forward_sorted(x, w, y, pos, ci, co)
+    unsorted = torch.tensor([[[2, 0, 4]]], dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="ascending"):
+        C.inf_dist_forward_sorted(x, w, y, pos, unsorted, co)
