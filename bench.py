@@ -686,8 +686,9 @@ def gpu_comparator_block(job, steps=10, warmup=3):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / n
 
-    # the faster of two blocks: on a freshly started machine the first block still pages code of the
-    # PyTorch operators the reference's sampler uses in from disk (seen: 125-180 ms against 40 ms)
+    # the faster of two blocks: the reference's step reads a count back from the GPU for every layer
+    # (its sampler's .item()), so its ~2000 launches per step are exposed to the host and the time
+    # swings with the load on the host's cores (seen: 40 ms on a quiet host, 79-182 ms on busy ones)
     ms_blocks = [timed(step, steps, warmup), timed(step, steps, 0)]
     ms_ref = min(ms_blocks)
     ms_ref_faithful = timed(lambda x, t: bound_pass(x, t, True), 3, 1)
